@@ -94,6 +94,7 @@ def lib() -> ctypes.CDLL:
     sig("cl_b200_copy_to_device_ptr", i32, vp, i32, i64, ctypes.c_uint64, i64, i32)
     sig("cl_b200_sm_count", i32, vp)
     sig("cl_b200_mem_free", i64, vp)
+    sig("cl_b200_stream_handle", i64, vp, i32)
     sig("cl_b200_last_error", cp)
     sig("cl_b200_argmax_noalloc", i32, vp, i32, i32, i32, vp, vp)
     sig("cl_b200_argmax_noalloc_error", cp)

@@ -86,7 +86,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         na_src = CSRC / "noalloc" / "argmax_noalloc.cu"
         na_obj = BUILD / "argmax_noalloc.o"
         log += _run([NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
-                     "-Xcompiler", "-fPIC", "-c", str(na_src), "-o", str(na_obj)])
+                     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-c", str(na_src), "-o", str(na_obj)])
         cuda_lib = str(Path(NVCC).resolve().parent.parent / "lib64")
         cmd = [CXX, "-shared", "-fPIC", "-O2", "-std=c++17", "-Wall", "-Wno-unused-function",
                "-fvisibility=hidden", "-I", str(ROOT / "include"), "-I", str(CSRC / "abi"),

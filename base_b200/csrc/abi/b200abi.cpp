@@ -766,6 +766,15 @@ int32_t cl_b200_copy_async(B200CudaContext *c, int32_t dst, int64_t doff, int32_
 
 int32_t cl_b200_device_ordinal(B200CudaContext *c) { return c ? c->ordinal : -1; }
 int32_t cl_b200_sm_count(B200CudaContext *c) { return c ? c->sm_count : -1; }
+// The CUstream behind a stream id (-1 = the main stream), as an integer; 0 for a bad id.
+int64_t cl_b200_stream_handle(B200CudaContext *c, int32_t stream_id) {
+  if (!c) { set_err("null context"); return 0; }
+  std::lock_guard<std::mutex> g(c->mu);
+  CUstream st = nullptr;
+  if (!get_stream(c, stream_id, &st)) { set_err("stream_handle: bad stream id"); return 0; }
+  return int64_t(reinterpret_cast<uintptr_t>(st));
+}
+
 int64_t cl_b200_mem_free(B200CudaContext *c) {
   if (!c) { set_err("null context"); return -1; }
   std::lock_guard<std::mutex> g(c->mu);

@@ -75,6 +75,10 @@ struct MegaArgs {
   int max_splits;
   int mx;          // 1: expert weights are in the wide block-scaled layout (moe_mx.cuh) and run on the tensor cores
   int kc_gu, kc_dn;   // its chunk sizes (K blocks per ring slot) for gate_up and down
+  // Failure-path test hooks (0 in production): the producers leave out ring fill number test_skip_fill - 1, so
+  // that the consumers' wait for it runs out; spin = iteration limit of every wait (0: kMegaSpin).
+  int test_skip_fill;
+  unsigned spin;
 };
 
 // One attention unit: kAttnSplit cache rows of a kv head (bf16, padded to 144
@@ -108,6 +112,7 @@ struct alignas(16) MegaSmem {
   float r_gate[kMegaMaxTopK];     // gate of top-k rank j
   int r_sel[kMegaMaxTopK];        // expert of top-k rank j
   int abort;
+  uint32_t spin;                  // iteration limit of every wait
   float racc[128];                // router partial sums of this CTA's o-proj rows, per expert
   float rrow[64];                 // h1 values of the super group being finished
   float am_v[2];
@@ -138,7 +143,7 @@ B200_DEVICE void cons_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kMegaConsThr
 
 // Bounded mbarrier wait that gives up quickly once the CTA is aborted.
 B200_DEVICE bool mega_wait(uint64_t *bar, uint32_t parity, MegaSmem *sm, int *status, int code) {
-  const uint32_t lim = *reinterpret_cast<volatile int *>(&sm->abort) ? 4096u : kMegaSpin;
+  const uint32_t lim = *reinterpret_cast<volatile int *>(&sm->abort) ? 4096u : sm->spin;
   for (uint32_t i = 0; i < lim; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 1023u) == 1023u && *reinterpret_cast<volatile int *>(status) != 0) break;   // another CTA gave up
@@ -159,6 +164,7 @@ struct MegaCtx {
   int nstamp;
   uint32_t ndone;      // block-scaled path: phases finished (parity of the `done` barrier)
   uint32_t nmx;        // block-scaled path: chunks handed from warp 4 to warp 0 so far (index and parity of `sready`)
+  uint32_t skip_fill;  // producer, test hook: 1 + the ring fill to leave out (0: none)
 };
 
 // Phase time stamp of this CTA (thread 0), when the host asked for a trace.
@@ -184,7 +190,7 @@ B200_DEVICE void grid_barrier(MegaCtx &c) {
     while (ld_acquire_u32(c.g->sync) < target) {
       ++it;
       if ((it & 63u) == 0 && *reinterpret_cast<volatile int *>(c.g->status) != 0) break;
-      if (it > kMegaSpin) { atomicCAS(c.g->status, 0, 10); break; }
+      if (it > c.sm->spin) { atomicCAS(c.g->status, 0, 10); break; }
     }
   }
   cons_sync();
@@ -204,6 +210,7 @@ B200_DEVICE void mega_fill(MegaCtx &c, const void *src0, uint32_t b0, const void
   const uint32_t slot = c.seq % kMegaSlots;
   if (c.seq >= kMegaSlots) mega_wait(&c.sm->empty[slot], ((c.seq / kMegaSlots) - 1) & 1, c.sm, c.g->status, 11);
   uint8_t *dst = c.ring + size_t(slot) * kMegaSlotBytes;
+  if (c.skip_fill && c.seq + 1 == c.skip_fill) { c.seq++; return; }      // test hook: this slot never fills
   mbar_expect_tx(&c.sm->full[slot], b0 + b1 + b2);
   bulk_g2s(dst, src0, b0, &c.sm->full[slot]);
   if (b1) bulk_g2s(dst + b0, src1, b1, &c.sm->full[slot]);
@@ -1242,6 +1249,7 @@ mega_decode(const MegaGlobals *__restrict__ gp, MegaArgs a) {
   c.nstamp = 0;
   c.ndone = 0;
   c.nmx = 0;
+  c.skip_fill = uint32_t(a.test_skip_fill);
   c.tid = threadIdx.x;
   c.lane = threadIdx.x & 31;
   c.warp = threadIdx.x >> 5;
@@ -1254,6 +1262,7 @@ mega_decode(const MegaGlobals *__restrict__ gp, MegaArgs a) {
     for (int i = 0; i < 3; ++i) mbar_init(&sm->done[i], 1);
     for (int i = 0; i < kMegaSlots; ++i) mbar_init(&sm->sready[i], 1);
     sm->abort = 0;
+    sm->spin = a.spin ? a.spin : kMegaSpin;
   }
   fence_barrier_init();
   if (a.mx && c.warp == 0) tc_alloc(&sm->tmem_base, 512);       // the only CTA on this SM: all of tensor memory

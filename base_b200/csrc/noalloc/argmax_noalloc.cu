@@ -16,6 +16,7 @@
 // two calls that overlap on the GPU (different streams, no ordering) race.
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdio>
 
 #include "../kernels/dense_decode.cuh"
@@ -34,7 +35,18 @@ static __device__ __align__(256) unsigned char g_argmax_scratch[kPartVBytes + kP
 
 // Device address of the scratch, per device ordinal.  In host code the name
 // g_argmax_scratch is only a handle for the runtime, never a device address.
-unsigned char *g_scratch_ptr[kNoAllocMaxDevices] = {};
+// The address belongs to the device's primary context; if the host program
+// resets the device it goes stale, which shows as an error of the first
+// operation on it: the entry point then looks it up again, once.
+std::atomic<unsigned char *> g_scratch_ptr[kNoAllocMaxDevices];
+
+unsigned char *resolve_scratch(int dev, cudaError_t *e) {
+  unsigned char *p = nullptr;
+  *e = cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_argmax_scratch);
+  if (*e != cudaSuccess || !p) return nullptr;
+  g_scratch_ptr[dev].store(p, std::memory_order_release);
+  return p;
+}
 
 thread_local char t_noalloc_err[256] = "";
 
@@ -51,7 +63,10 @@ extern "C" __attribute__((visibility("default"))) const char *cl_b200_argmax_noa
 
 // out_dev[b] = smallest index of the maximum of logits_dev[b * stride .. + vocab), b < tokens.
 // All pointers are device pointers on the current device; `stream` is a
-// cudaStream_t / CUstream (null = the legacy default stream).
+// cudaStream_t / CUstream (null = the legacy default stream).  Everything
+// runs on that stream: to order the call after logits this library produced,
+// pass the producing stream's handle (cl_b200_stream_handle), because the
+// library's streams do not synchronise with the default stream.
 // The first call on a device looks up the scratch address (one
 // cudaGetSymbolAddress); make that first call outside any stream capture.
 extern "C" __attribute__((visibility("default"))) int32_t
@@ -68,19 +83,21 @@ cl_b200_argmax_noalloc(const float *logits_dev, int32_t vocab, int32_t tokens, i
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return fail("cudaGetDevice", e);
   if (dev < 0 || dev >= kNoAllocMaxDevices) return fail("device ordinal out of range", cudaSuccess);
-  if (!g_scratch_ptr[dev]) {
-    unsigned char *p = nullptr;
-    e = cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_argmax_scratch);
-    if (e != cudaSuccess || !p) return fail("cudaGetSymbolAddress", e);
-    g_scratch_ptr[dev] = p;
+  unsigned char *base = g_scratch_ptr[dev].load(std::memory_order_acquire);
+  if (!base && !(base = resolve_scratch(dev, &e))) return fail("cudaGetSymbolAddress", e);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  e = cudaMemsetAsync(base + kPartVBytes + kPartIBytes, 0, kTicketBytes, st);
+  if (e != cudaSuccess) {
+    // a remembered address from before a device reset: look it up again, once
+    (void)cudaGetLastError();
+    cudaError_t e2;
+    if (!(base = resolve_scratch(dev, &e2))) return fail("cudaGetSymbolAddress", e2);
+    e = cudaMemsetAsync(base + kPartVBytes + kPartIBytes, 0, kTicketBytes, st);
+    if (e != cudaSuccess) return fail("cudaMemsetAsync", e);
   }
-  unsigned char *base = g_scratch_ptr[dev];
   float *part_v = reinterpret_cast<float *>(base);
   int *part_i = reinterpret_cast<int *>(base + kPartVBytes);
   int *tickets = reinterpret_cast<int *>(base + kPartVBytes + kPartIBytes);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  e = cudaMemsetAsync(tickets, 0, kTicketBytes, st);
-  if (e != cudaSuccess) return fail("cudaMemsetAsync", e);
   ArgmaxArgs a{vocab, tokens, stride, kNoAllocParts};
   argmax_first<<<dim3(kNoAllocParts, tokens, 1), 256, 0, st>>>(logits_dev, out_dev, nullptr, nullptr, part_v, part_i,
                                                                tickets, a);

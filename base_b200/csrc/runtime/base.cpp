@@ -8,6 +8,8 @@
 
 #include <algorithm>
 #include <cctype>
+#include <cerrno>
+#include <climits>
 #include <cstdlib>
 #include <map>
 #include <memory>
@@ -41,6 +43,8 @@ struct JVal {
   bool b = false;
   double num = 0;
   int64_t inum = 0;
+  uint64_t unum = 0;
+  bool neg = false;
   bool is_int = false;
   std::string str;
   std::vector<JVal> arr;
@@ -89,7 +93,17 @@ struct JParser {
     ++p;
     return true;
   }
+  // Containers nest at most kMaxDepth deep (an artifact needs 5): the parser recurses once per level.
+  static constexpr int kMaxDepth = 64;
+  int depth = 0;
   bool parse(JVal &v) {
+    if (depth >= kMaxDepth) return fail("nesting too deep");
+    ++depth;
+    const bool ok = parse_inner(v);
+    --depth;
+    return ok;
+  }
+  bool parse_inner(JVal &v) {
     ws();
     if (p >= end) return fail("unexpected end");
     char c = *p;
@@ -143,7 +157,14 @@ struct JParser {
       v.kind = JVal::Num;
       v.is_int = is_int;
       v.num = strtod(t.c_str(), nullptr);
-      if (is_int) v.inum = strtoll(t.c_str(), nullptr, 10);
+      if (is_int) {
+        // unsigned fields (memory_size, offsets) may exceed 2^63 - 1: keep the exact value or reject
+        errno = 0;
+        if (t[0] == '-') { v.inum = strtoll(t.c_str(), nullptr, 10); v.neg = true; }
+        else v.unum = strtoull(t.c_str(), nullptr, 10);
+        if (errno == ERANGE) return fail("integer out of range");
+        if (!v.neg) v.inum = v.unum > uint64_t(INT64_MAX) ? INT64_MAX : int64_t(v.unum);
+      }
       return true;
     }
     return fail("unexpected character");
@@ -177,8 +198,8 @@ struct B200Base {
 namespace {
 
 bool get_u64(const JVal *v, uint64_t *out) {
-  if (!v || v->kind != JVal::Num || !v->is_int || v->inum < 0) return false;
-  *out = uint64_t(v->inum);
+  if (!v || v->kind != JVal::Num || !v->is_int || v->neg) return false;
+  *out = v->unum;
   return true;
 }
 
@@ -325,6 +346,9 @@ B200Base *b200_base_new(const char *cranelift_ir, uint64_t memory_size, const ui
   if (header_end < io_offsets[3]) header_end = UINT64_MAX;  // saturating, base/src/lib.rs:37-40
   uint64_t needed = std::max(std::max(memory_size, initial_len), header_end);
   if (plugin) needed = std::max(needed, kMinNativeMemory);
+  // The reference aborts when such a resize cannot be served (base/src/lib.rs:36-52); here it is an error.
+  // The cap also keeps the rounding below from wrapping.
+  if (needed > (uint64_t(1) << 40)) return fail(B200_ERR_EXECUTION, "memory_size beyond 1 TiB");
   for (int i = 0; i < 4; ++i)
     if (io_offsets[i] > needed - 8) return fail(B200_ERR_EXECUTION, "io offset outside memory");
   // Page-locked for the life of the Base, like the reference's pinned box.

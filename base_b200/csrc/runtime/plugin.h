@@ -75,6 +75,54 @@ struct StageIO {
 // Record a stage failure: status word + thread-local message.
 void stage_fail(uint8_t *mem, int64_t code, const std::string &msg);
 
+// What a `load` stage creates, so that a failed load leaves nothing behind and a
+// later destroy frees exactly what this stage made.  The CUDA context at
+// mem+0x10 may belong to the caller (it was there before `load`): then only the
+// buffers created between begin() and seal() are this stage's, identified by
+// their ids (ids are sequential and never reused, base/src/ffi/cuda.rs:360-381).
+struct LoadScope {
+  uint8_t *mem;
+  bool created_ctx = false;
+  int first_buf = -1, last_buf = -2;      // inclusive id range of this load's buffers
+  std::vector<int> pinned, events, graphs;
+
+  static int probe_id(B200CudaContext *ctx) {
+    const int id = cl_cuda_create_buffer(ctx, 4);
+    if (id >= 0) cl_cuda_free_buffer(ctx, id);
+    return id;
+  }
+  // Context (created when the slot is empty) and the id watermark.  False: nothing to undo.
+  bool begin(uint8_t *m) {
+    mem = m;
+    StageIO io(m);
+    if (!io.ctx()) {
+      cl_cuda_init(io.ctx_slot());
+      if (!io.ctx()) return false;
+      created_ctx = true;
+    }
+    first_buf = probe_id(io.ctx()) + 1;
+    return first_buf > 0;
+  }
+  void seal() { last_buf = probe_id(StageIO(mem).ctx()) - 1; }
+  // Free everything made since begin(): the whole context when this stage created it.
+  void release() {
+    StageIO io(mem);
+    B200CudaContext *ctx = io.ctx();
+    if (!ctx) return;
+    if (created_ctx) { cl_cuda_cleanup(io.ctx_slot()); return; }
+    cl_cuda_stream_sync(ctx, -1);
+    if (last_buf < first_buf) seal();
+    for (int g : graphs) cl_cuda_graph_destroy(ctx, g);
+    for (int id = first_buf; id <= last_buf; ++id) cl_cuda_free_buffer(ctx, id);   // ids freed earlier just answer -1
+    for (int p : pinned) cl_cuda_pinned_free(ctx, p);
+    for (int e : events) cl_cuda_event_destroy(ctx, e);
+  }
+  void fail(int64_t code, const std::string &msg) {
+    release();
+    stage_fail(mem, code, msg);
+  }
+};
+
 // Launch helper over cl_b200_launch with the built-in module.
 struct Launcher {
   B200CudaContext *ctx;

@@ -42,7 +42,11 @@ struct GptOssHeader {
                          // bit 5: the whole step as one persistent kernel (batch 1)
                          // bit 6: with bit 5, the experts run on the block-scaled tensor cores (mx tiles, moe_mx.cuh)
   uint32_t expert_lo, expert_n;   // experts resident on this rank (expert_n = 0: all)
-  uint32_t reserved[11];
+  // Failure-path test hooks of the persistent step kernel (0 in production): 1 + the ring fill its producers
+  // leave out, and the iteration limit of its waits (0: the default).  With a fill left out the consumers'
+  // bounded wait runs out, the kernel stores a status code and ends, and `infer` reports it.
+  uint32_t test_skip_fill, test_spin;
+  uint32_t reserved[9];
 };
 static_assert(sizeof(GptOssHeader) == 128, "header is 128 bytes");
 constexpr uint32_t kMagic = 0x31534f47;  // "GOS1"
@@ -66,6 +70,8 @@ struct MegaArgs {
   float eps, alpha, limit, attn_scale;
   int max_splits;
   int mx, kc_gu, kc_dn;
+  int test_skip_fill;
+  unsigned spin;
 };
 constexpr int kMegaThreads = 512;
 constexpr int kMegaSmemBytes = 7 * 25088 + 56832;   // ring + MegaSmem (mega_decode.cuh): all 227 KB
@@ -103,7 +109,9 @@ struct State {
   int max_decode = 4096;
   int dense_stream = 1, dense_stages = 4, dense_ctas = 296;
   int mega = 0, mega_tab = -1, mega_sync = -1, mega_am_v = -1, mega_am_i = -1, mega_grid = 0, mega_trace = -1, mega_rpart = -1, mega_mx = 0, mega_kc_gu = 8, mega_kc_dn = 8;
-  bool owns_ctx = false;
+  LoadScope scope;
+  int fail_after = -1;
+  std::vector<int64_t> next_pos;     // per sequence: the position the next step will run at (-1: prep has not run)
 };
 
 bool synth(B200CudaContext *ctx, Launcher &L, int buf, uint64_t n, uint32_t layer, uint32_t kind, uint32_t seed,

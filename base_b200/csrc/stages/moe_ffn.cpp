@@ -86,7 +86,7 @@ struct State {
   int gu_mx = -1, dn_mx = -1;      // mx tiles of the block-scaled tensor-core path (flags bit 6)
   int warps_gu = 4, warps_dn = 4, cta_target = 100000, ring_stages = 2;
   int T = 0;
-  bool owns_ctx = false;
+  LoadScope scope;
 };
 
 bool upload_part(B200CudaContext *ctx, int *id, const uint8_t *&p, const uint8_t *end, uint64_t bytes) {
@@ -205,9 +205,12 @@ bool retile(B200CudaContext *ctx, Launcher &L, int *codes, int *scales, int flag
   return true;
 }
 
+void destroy(uint8_t *mem);
+
+// load on a loaded instance releases what the earlier load made and loads anew.
 void stage_load(uint8_t *mem) {
   StageIO io(mem);
-  if (io.state<State>()) return stage_fail(mem, 1, "load: already loaded");
+  if (io.state<State>()) destroy(mem);
   if (io.data_len < sizeof(MoeLoadHeader)) return stage_fail(mem, 1, "load: payload shorter than header");
   MoeLoadHeader h;
   memcpy(&h, io.data, sizeof(h));
@@ -228,16 +231,20 @@ void stage_load(uint8_t *mem) {
     return stage_fail(mem, 1, "load: payload is " + std::to_string(io.data_len) + " bytes, expected " +
                                    std::to_string(need));
   }
-  if (!io.ctx()) {
-    cl_cuda_init(io.ctx_slot());
-    if (!io.ctx()) return stage_fail(mem, 2, std::string("load: no CUDA device: ") + cl_b200_last_error());
-  }
+  // the rest of the request is checked before anything is allocated
+  if ((h.flags & 32) && ((2 * I) % 192 || H % 192 || H % 64 || I % 64))
+    return stage_fail(mem, 1, "load: the tensor-core path needs hidden and 2*inter to be multiples of 192 and of 64");
+  if ((h.flags & 64) && (H % 64 || I % 64 || H > 2880 || I > 2880 || (h.flags & 2)))
+    return stage_fail(mem, 1, "load: the block-scaled path needs hidden and inter to be multiples of 64, at most 2880, and the tiled layout");
+  if ((h.flags & 32) && (h.flags & 2))
+    return stage_fail(mem, 1, "load: the tensor-core path needs the tiled layout (flags bit 1 must be clear)");
+  LoadScope scope;
+  if (!scope.begin(mem)) return stage_fail(mem, 2, std::string("load: no CUDA device: ") + cl_b200_last_error());
   B200CudaContext *ctx = io.ctx();
   std::unique_ptr<State> s(new State());
   s->h = h;
-  s->owns_ctx = true;
   s->module = cl_b200_builtin_module(ctx);
-  if (s->module < 0) return stage_fail(mem, 2, std::string("load: kernel image: ") + cl_b200_last_error());
+  if (s->module < 0) return scope.fail(2, std::string("load: kernel image: ") + cl_b200_last_error());
   const uint8_t *p = io.data + sizeof(h), *end = io.data + io.data_len;
   bool ok = upload_part(ctx, &s->Wr, p, end, ER * H * 4) && upload_part(ctx, &s->br, p, end, ER * 4) &&
             upload_part(ctx, &s->gu_codes, p, end, E * 2 * I * (H / 2)) &&
@@ -262,17 +269,13 @@ void stage_load(uint8_t *mem) {
        (s->status = cl_cuda_create_buffer(ctx, 4)) >= 0 && (s->x1 = cl_cuda_create_buffer(ctx, H * 4)) >= 0 &&
        (s->ticket = cl_cuda_create_buffer(ctx, 4)) >= 0 &&
        (s->tiles = cl_cuda_create_buffer(ctx, (1 + 3 * (T * k / 128 + ER + 1)) * 4)) >= 0;
-  if ((h.flags & 32) && ((2 * I) % 192 || H % 192 || H % 64 || I % 64))
-    return stage_fail(mem, 1, "load: the tensor-core path needs hidden and 2*inter to be multiples of 192 and of 64");
   if (const char *e = getenv("B200_MOE_WARPS_GU")) s->warps_gu = std::max(1, std::min(16, atoi(e)));
   if (const char *e = getenv("B200_MOE_WARPS_DN")) s->warps_dn = std::max(1, std::min(16, atoi(e)));
   if (const char *e = getenv("B200_MOE_CTA_TARGET")) s->cta_target = std::max(1, atoi(e));
   if (const char *e = getenv("B200_MOE_RING")) s->ring_stages = std::max(1, std::min(8, atoi(e)));
-  if (!ok) return stage_fail(mem, 2, std::string("load: device allocation/upload failed: ") + cl_b200_last_error());
+  if (!ok) return scope.fail(2, std::string("load: device allocation/upload failed: ") + cl_b200_last_error());
 
   if (h.flags & 64) {
-    if (H % 64 || I % 64 || H > 2880 || I > 2880 || (h.flags & 2))
-      return stage_fail(mem, 1, "load: the block-scaled path needs hidden and inter to be multiples of 64, at most 2880, and the tiled layout");
     Launcher L{ctx, s->module};
     auto make = [&](int codes, int scales, int R, int K) {
       const int64_t blocks = int64_t(E) * (R / 32) * 2;
@@ -285,7 +288,7 @@ void stage_load(uint8_t *mem) {
     s->gu_mx = make(s->gu_codes, s->gu_scales, int(2 * I), int(H));
     s->dn_mx = make(s->dn_codes, s->dn_scales, int(H), int(I));
     if (s->gu_mx < 0 || s->dn_mx < 0)
-      return stage_fail(mem, 2, "load: building the mx tiles failed: " + (L.ok ? std::string(cl_b200_last_error()) : L.err));
+      return scope.fail(2, "load: building the mx tiles failed: " + (L.ok ? std::string(cl_b200_last_error()) : L.err));
   }
   const bool want_tiled = !(h.flags & 2) && H % 64 == 0 && I % 64 == 0;
   if (want_tiled) {
@@ -297,7 +300,7 @@ void stage_load(uint8_t *mem) {
     int gc = s->gu_codes, gs = s->gu_scales, dc = s->dn_codes, ds = s->dn_scales;
     bool done = flag_buf >= 0 && retile(ctx, L, &gc, &gs, flag_buf, int(E), int(2 * I), int(H)) &&
                 retile(ctx, L, &dc, &ds, flag_buf, int(E), int(H), int(I));
-    if (!done) return stage_fail(mem, 2, "load: re-tiling failed: " + (L.ok ? std::string(cl_b200_last_error()) : L.err));
+    if (!done) return scope.fail(2, "load: re-tiling failed: " + (L.ok ? std::string(cl_b200_last_error()) : L.err));
     int32_t flag = 0;
     cl_cuda_download_ptr(ctx, flag_buf, reinterpret_cast<uint8_t *>(&flag), 4);
     cl_cuda_free_buffer(ctx, flag_buf);
@@ -305,7 +308,7 @@ void stage_load(uint8_t *mem) {
     if (flag == 0) {
       s->tiled = true;
     } else if (h.flags & 32) {
-      return stage_fail(mem, 1, "load: the tensor-core path needs the tiled layout (scale bytes 1..254)");
+      return scope.fail(1, "load: the tensor-core path needs the tiled layout (scale bytes 1..254)");
     } else {
       // Put the checkpoint layout back from the host payload.
       const uint8_t *q = io.data + sizeof(h) + ER * H * 4 + ER * 4;
@@ -316,7 +319,9 @@ void stage_load(uint8_t *mem) {
     }
   }
   if ((h.flags & 32) && !s->tiled)
-    return stage_fail(mem, 1, "load: the tensor-core path needs the tiled layout (flags bit 1 must be clear)");
+    return scope.fail(1, "load: the tensor-core path needs the tiled layout (hidden and inter multiples of 64)");
+  scope.seal();
+  s->scope = scope;
   io.set_state(s.release());
 }
 
@@ -522,7 +527,8 @@ void destroy(uint8_t *mem) {
   StageIO io(mem);
   State *s = io.state<State>();
   if (s) {
-    if (s->owns_ctx) cl_cuda_cleanup(io.ctx_slot());
+    if (s->ev0 >= 0) s->scope.events = {s->ev0, s->ev1};
+    s->scope.release();
     delete s;
     io.set_state(nullptr);
   }

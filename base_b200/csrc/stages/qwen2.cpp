@@ -63,6 +63,8 @@ struct State {
   int pin_in = -1, pin_out = -1, graph = -1, ev0 = -1, ev1 = -1;
   int max_splits = 1, max_decode = 4096;
   int dense_stream = 1;
+  LoadScope scope;
+  std::vector<int64_t> next_pos;     // per sequence: the position the next step runs at
 };
 
 constexpr int kArgmaxParts = 128;
@@ -125,9 +127,12 @@ void enqueue_step(State *s, Launcher &L) {
 
 void stage_noop(uint8_t *) {}
 
+void destroy(uint8_t *mem);
+
+// load on a loaded instance releases what the earlier load made and loads anew.
 void stage_load(uint8_t *mem) {
   StageIO io(mem);
-  if (io.state<State>()) return stage_fail(mem, 1, "load: already loaded");
+  if (io.state<State>()) destroy(mem);
   if (io.data_len != sizeof(QwenHeader)) return stage_fail(mem, 1, "load: payload must be the 64-byte header");
   QwenHeader h;
   memcpy(&h, io.data, sizeof(h));
@@ -140,15 +145,13 @@ void stage_load(uint8_t *mem) {
   if (h.batch == 0 || h.batch > 4 || h.layers == 0 || h.layers > 128 || h.vocab == 0 || h.max_seq == 0 ||
       h.max_seq > (1u << 20))
     return stage_fail(mem, 1, "load: batch 1..4, layers/vocab/max_seq in range");
-  if (!io.ctx()) {
-    cl_cuda_init(io.ctx_slot());
-    if (!io.ctx()) return stage_fail(mem, 2, std::string("load: no CUDA device: ") + cl_b200_last_error());
-  }
+  LoadScope scope;
+  if (!scope.begin(mem)) return stage_fail(mem, 2, std::string("load: no CUDA device: ") + cl_b200_last_error());
   B200CudaContext *ctx = io.ctx();
   std::unique_ptr<State> s(new State());
   s->h = h;
   s->module = cl_b200_builtin_module(ctx);
-  if (s->module < 0) return stage_fail(mem, 2, std::string("load: kernel image: ") + cl_b200_last_error());
+  if (s->module < 0) return scope.fail(2, std::string("load: kernel image: ") + cl_b200_last_error());
   if (const char *e = getenv("B200_DENSE_STREAM")) s->dense_stream = atoi(e);
   const uint64_t H = h.hidden, F = h.inter, B = h.batch, V = h.vocab;
   const uint64_t QD = uint64_t(h.n_q) * 64, KVD = uint64_t(h.n_kv) * 64, QKV = QD + 2 * KVD;
@@ -156,7 +159,7 @@ void stage_load(uint8_t *mem) {
   Launcher L{ctx, s->module};
   s->embed = alloc(ctx, V * H * 4, &ok);
   s->lnf = alloc(ctx, H * 4, &ok);
-  if (!ok) return stage_fail(mem, 2, std::string("load: allocation failed: ") + cl_b200_last_error());
+  if (!ok) return scope.fail(2, std::string("load: allocation failed: ") + cl_b200_last_error());
   synth(L, s->embed, V * H, 1000, kEmbed, h.seed, 2, 0.02);
   synth(L, s->lnf, H, 1000, kLnF, h.seed, 4, 0.02);
   s->layers.resize(h.layers);
@@ -181,7 +184,7 @@ void stage_load(uint8_t *mem) {
     synth(L, ly.wdn, H * F, l, kWdn, h.seed, 2, 0.02);
   }
   if (!ok || !L.ok || cl_cuda_stream_sync(ctx, -1) != 0)
-    return stage_fail(mem, 2, "load: weight generation failed: " + (L.ok ? std::string(cl_b200_last_error()) : L.err));
+    return scope.fail(2, "load: weight generation failed: " + (L.ok ? std::string(cl_b200_last_error()) : L.err));
   {
     const int half = 32;
     std::vector<float> tab(size_t(2) * h.max_seq * half);
@@ -217,7 +220,11 @@ void stage_load(uint8_t *mem) {
   s->ev0 = cl_cuda_event_create(ctx);
   s->ev1 = cl_cuda_event_create(ctx);
   if (!ok || s->pin_in < 0 || s->pin_out < 0)
-    return stage_fail(mem, 2, std::string("load: allocation failed: ") + cl_b200_last_error());
+    return scope.fail(2, std::string("load: allocation failed: ") + cl_b200_last_error());
+  scope.pinned = {s->pin_in, s->pin_out};
+  scope.events = {s->ev0, s->ev1};
+  scope.seal();
+  s->scope = scope;
   io.set_state(s.release());
 }
 
@@ -249,6 +256,25 @@ void stage_prep(uint8_t *mem) {
   memcpy(pin, io.data, io.data_len);
   if (cl_cuda_upload_ptr_async(io.ctx(), s->meta, pin, int64_t(io.data_len), -1) != 0)
     return stage_fail(mem, 2, std::string("prep: upload: ") + cl_b200_last_error());
+  s->next_pos.assign(s->h.batch, -1);
+  for (uint32_t b = 0; b < s->h.batch; ++b) {
+    uint32_t pos;
+    memcpy(&pos, io.data + 8 * b + 4, 4);
+    s->next_pos[b] = pos;
+  }
+}
+
+// The device advances the positions itself; the host mirrors them so that a step past the end of the
+// cache and of the RoPE table is refused.
+bool room_for(State *s, uint32_t n, std::string *why) {
+  if (s->next_pos.size() != s->h.batch) { *why = "prep has not run"; return false; }
+  for (int64_t p : s->next_pos)
+    if (p < 0 || p + int64_t(n) > int64_t(s->h.max_seq)) {
+      *why = "position " + std::to_string(p) + " + " + std::to_string(n) + " steps is out of range (max_seq " +
+             std::to_string(s->h.max_seq) + ")";
+      return false;
+    }
+  return true;
 }
 
 void stage_infer(uint8_t *mem) {
@@ -263,9 +289,11 @@ void stage_infer(uint8_t *mem) {
   const uint64_t ob = uint64_t(s->h.batch) * 4;
   if (io.out_len != 0 && io.out_len != ob) return stage_fail(mem, 1, "infer: out must be one u32 per sequence");
   std::string err;
+  if (!room_for(s, 1, &err)) return stage_fail(mem, 1, "infer: " + err);
   if (!ensure_graph(s, ctx, &err)) return stage_fail(mem, 2, "infer: graph capture: " + err);
   if (cl_cuda_graph_launch(ctx, s->graph, -1) != 0)
     return stage_fail(mem, 2, std::string("infer: graph launch: ") + cl_b200_last_error());
+  for (int64_t &p : s->next_pos) p += 1;
   uint8_t *pout = reinterpret_cast<uint8_t *>(cl_cuda_pinned_ptr(ctx, s->pin_out));
   cl_cuda_download_ptr_async(ctx, s->status, pout + 32, 4, -1);
   if (io.out_len) cl_cuda_download_ptr_async(ctx, s->next_tok, pout, int64_t(ob), -1);
@@ -289,6 +317,7 @@ void stage_decode(uint8_t *mem) {
   if (io.out_len != 0 && io.out_len != tb && io.out_len != tb + 4)
     return stage_fail(mem, 1, "decode: out must be empty, tokens, or tokens + 4 bytes");
   std::string err;
+  if (!room_for(s, n, &err)) return stage_fail(mem, 1, "decode: " + err);
   if (!ensure_graph(s, ctx, &err)) return stage_fail(mem, 2, "decode: graph capture: " + err);
   const int64_t row = int64_t(s->h.batch) * 4;
   cl_cuda_event_record(ctx, s->ev0, -1);
@@ -297,6 +326,7 @@ void stage_decode(uint8_t *mem) {
         cl_b200_copy_async(ctx, s->tokens_out, int64_t(i) * row, s->next_tok, 0, row, -1) != 0)
       return stage_fail(mem, 2, std::string("decode: launch: ") + cl_b200_last_error());
   cl_cuda_event_record(ctx, s->ev1, -1);
+  for (int64_t &p : s->next_pos) p += n;
   if (cl_cuda_stream_sync(ctx, -1) != 0) return stage_fail(mem, 3, std::string("decode: sync: ") + cl_b200_last_error());
   int32_t st = 0;
   if (cl_cuda_download_ptr(ctx, s->status, reinterpret_cast<uint8_t *>(&st), 4) != 0 || st != 0)
@@ -344,7 +374,8 @@ void destroy(uint8_t *mem) {
   StageIO io(mem);
   State *s = io.state<State>();
   if (s) {
-    cl_cuda_cleanup(io.ctx_slot());
+    if (s->graph >= 0) s->scope.graphs.push_back(s->graph);
+    s->scope.release();
     delete s;
     io.set_state(nullptr);
   }

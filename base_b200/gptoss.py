@@ -42,12 +42,14 @@ class GptOssConfig:
     limit: float = 7.0
     seed: int = 0
     flags: int = PDL
+    test_skip_fill: int = 0   # failure-path test hook: 1 + the ring fill the persistent kernel's producers leave out
+    test_spin: int = 0        # failure-path test hook: iteration limit of the persistent kernel's waits (0: default)
 
     def header(self) -> bytes:
-        h = struct.pack("<13I4f4I11I", MAGIC, self.layers, self.hidden, self.inter, self.experts, self.top_k,
+        h = struct.pack("<13I4f4I2I9I", MAGIC, self.layers, self.hidden, self.inter, self.experts, self.top_k,
                         self.n_q, self.n_kv, self.head_dim, self.vocab, self.window, self.max_seq, self.batch,
                         self.rope_theta, self.eps, self.alpha, self.limit, self.seed, self.flags, 0, 0,
-                        *([0] * 11))
+                        self.test_skip_fill, self.test_spin, *([0] * 9))
         assert len(h) == 128
         return h
 
@@ -111,6 +113,11 @@ class GptOss:
         if timed:
             return toks, struct.unpack("<f", bytes(out[nb:]))[0]
         return toks
+
+    def fill_kv(self):
+        """Overwrite every layer's KV cache with the seeded synthetic rows (stage `fillKV`), so that a step at a
+        late position has a full context without feeding the prompt."""
+        self.base.execute(self.art.extras["fillKV"], b"")
 
     def trace(self, n_ctas: int) -> np.ndarray:
         """Phase time stamps (ns) of the last persistent step: u64 [n_ctas][512], n_ctas = SM count."""

@@ -186,6 +186,12 @@ int32_t cl_b200_device_ordinal(B200CudaContext *ctx);
 int32_t cl_b200_sm_count(B200CudaContext *ctx);
 int64_t cl_b200_mem_free(B200CudaContext *ctx);
 
+/* The CUstream / cudaStream_t behind a stream id of this context (-1 = the main stream), as an
+ * integer; 0 for a bad id.  For handing a stream of this library to code that takes raw stream
+ * handles (cl_b200_argmax_noalloc below, another library in the process).  Every stream of this
+ * library is non-blocking: work on the legacy default stream (handle 0) is NOT ordered with it. */
+int64_t cl_b200_stream_handle(B200CudaContext *ctx, int32_t stream_id);
+
 /* Last error text of the calling thread ("" if none); never null. */
 const char *cl_b200_last_error(void);
 
@@ -201,7 +207,15 @@ const char *cl_b200_last_error(void);
  * that loads the library until exit; tokens <= 64, more is rejected with -1.
  * Calls share that array: calls that overlap on the GPU race.  The first
  * call on a device resolves the array's device address; make it before any
- * stream capture.  Returns 0, or -1 with text in cl_b200_argmax_noalloc_error(). */
+ * stream capture.  The address is remembered per device: after a
+ * cudaDeviceReset by the host program it is looked up again when the first
+ * operation on it fails.
+ * Ordering: the work runs on `stream` and nowhere else.  Logits produced by
+ * this library (cl_b200_launch, a stage program) are on one of its own
+ * non-blocking streams, with which the default stream does not synchronise:
+ * pass cl_b200_stream_handle(ctx, id) of the producing stream (-1 = main
+ * stream), or cl_cuda_sync on both sides of the call.
+ * Returns 0, or -1 with text in cl_b200_argmax_noalloc_error(). */
 int32_t cl_b200_argmax_noalloc(const float *logits_dev, int32_t vocab, int32_t tokens, int32_t stride,
                                int32_t *out_dev, void *stream);
 const char *cl_b200_argmax_noalloc_error(void);

@@ -27,6 +27,10 @@ def lib():
         _lib = ctypes.CDLL(str(LIB))
         _lib.oracle_moe_ffn.restype = ctypes.c_int
         _lib.oracle_max_threads.restype = ctypes.c_int
+        _lib.oracle_gptoss_new.restype = ctypes.c_void_p
+        _lib.oracle_qwen2_new.restype = ctypes.c_void_p
+        _lib.oracle_gptoss_step.restype = ctypes.c_int
+        _lib.oracle_qwen2_step.restype = ctypes.c_int
     return _lib
 
 
@@ -59,3 +63,84 @@ def moe_ffn(x: np.ndarray, p: dict, threads: int = 0):
 
 def max_threads() -> int:
     return lib().oracle_max_threads()
+
+
+class GptOssC:
+    """oracle/model_oracle.c: one sequence of a gpt-oss-architecture model with the seeded synthetic
+    weights, greedy decode token by token (same contract as oracle.gptoss_oracle.Model)."""
+
+    def __init__(self, c, threads: int = 0):
+        L = lib()
+        ci = (ctypes.c_int32 * 10)(c.layers, c.hidden, c.inter, c.experts, c.top_k, c.n_q, c.n_kv, c.vocab, c.window, c.max_seq)
+        cf = (ctypes.c_float * 4)(c.rope_theta, c.eps, c.alpha, c.limit)
+        self.c, self.L, self.threads = c, L, threads
+        self.h = L.oracle_gptoss_new(ci, cf, ctypes.c_uint32(c.seed), threads)
+        if not self.h:
+            raise MemoryError("oracle_gptoss_new failed")
+
+    def fill_kv(self, seq: int = 0, batch: int = 1):
+        self.L.oracle_gptoss_fill_kv(ctypes.c_void_p(self.h), seq, batch)
+
+    def step(self, token: int, pos: int, return_logits=False):
+        logits = np.empty(self.c.vocab, dtype=np.float32) if return_logits else None
+        nxt = self.L.oracle_gptoss_step(ctypes.c_void_p(self.h), int(token), int(pos), _p(logits) if return_logits else None, self.threads)
+        if nxt < 0:
+            raise RuntimeError("oracle_gptoss_step failed")
+        return (nxt, logits) if return_logits else nxt
+
+    def stats(self) -> dict:
+        out = np.zeros(4 + 8 * self.c.layers, dtype=np.float64)
+        self.L.oracle_gptoss_stats(ctypes.c_void_p(self.h), _p(out))
+        return {"dense_s": out[0], "attention_s": out[1], "moe_s": out[2], "head_s": out[3],
+                "experts": out[4:].astype(np.int64).reshape(self.c.layers, 8)[:, :self.c.top_k]}
+
+    def close(self):
+        if self.h:
+            self.L.oracle_gptoss_free(ctypes.c_void_p(self.h))
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Qwen2C:
+    """oracle/model_oracle.c: Qwen2-architecture greedy decode (f32), as oracle.qwen2_oracle.Model."""
+
+    def __init__(self, c, threads: int = 0):
+        L = lib()
+        ci = (ctypes.c_int32 * 7)(c.layers, c.hidden, c.inter, c.n_q, c.n_kv, c.vocab, c.max_seq)
+        cf = (ctypes.c_float * 2)(c.rope_theta, c.eps)
+        self.c, self.L, self.threads = c, L, threads
+        self.h = L.oracle_qwen2_new(ci, cf, ctypes.c_uint32(c.seed), threads)
+        if not self.h:
+            raise MemoryError("oracle_qwen2_new failed")
+
+    def step(self, token: int, pos: int, return_logits=False):
+        logits = np.empty(self.c.vocab, dtype=np.float32) if return_logits else None
+        nxt = self.L.oracle_qwen2_step(ctypes.c_void_p(self.h), int(token), int(pos), _p(logits) if return_logits else None, self.threads)
+        if nxt < 0:
+            raise RuntimeError("oracle_qwen2_step failed")
+        return (nxt, logits) if return_logits else nxt
+
+    def close(self):
+        if self.h:
+            self.L.oracle_qwen2_free(ctypes.c_void_p(self.h))
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def rowdot_gemv(W: np.ndarray, x: np.ndarray, threads: int = 1) -> np.ndarray:
+    """The reference's CPU GEMV fold (RowDotBenchAlgorithm.lean:20-150) over W [rows][K] f32."""
+    W = np.ascontiguousarray(W, dtype=np.float32)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    y = np.empty(W.shape[0], dtype=np.float32)
+    lib().oracle_rowdot_gemv_f32(_p(W), _p(x), _p(y), W.shape[0], W.shape[1], threads)
+    return y

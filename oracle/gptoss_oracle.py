@@ -148,10 +148,27 @@ class Model:
         self.v = [np.zeros((c.n_kv, 0, 64), dtype=np.float32) for _ in range(c.layers)]
         self.deq = {}
 
-    def _experts(self, l, ly):
-        if l not in self.deq:
-            self.deq[l] = (mo.mx_dequant(ly["gu_codes"], ly["gu_scales"]), mo.mx_dequant(ly["dn_codes"], ly["dn_scales"]))
-        return self.deq[l]
+    def _expert(self, l, ly, e):
+        """Dequantised (gate_up, down) matrices of expert e of layer l, a few kept."""
+        if (l, e) not in self.deq:
+            if len(self.deq) >= 16:
+                self.deq.pop(next(iter(self.deq)))
+            self.deq[(l, e)] = (mo.mx_dequant(ly["gu_codes"][e], ly["gu_scales"][e]),
+                                mo.mx_dequant(ly["dn_codes"][e], ly["dn_scales"][e]))
+        return self.deq[(l, e)]
+
+    def fill_kv(self, n_pos: int, seq: int = 0):
+        """The synthetic cache the stage program's `fillKV` extra writes, for positions < n_pos: every K/V row
+        is bf16 N(0, 1) from (seed, layer * 32 + 19 / 20, index in [batch][n_kv][cache_len][64]); position p of a
+        sliding layer sits in row p % cache_len."""
+        c = self.c
+        for l, ly in enumerate(self.w["layers"]):
+            cache_len = min(ly["window"], c.max_seq) if ly["window"] > 0 else c.max_seq
+            n = c.n_kv * cache_len * 64
+            rows = np.arange(n_pos) % cache_len
+            for kind, dst in ((19, self.k), (20, self.v)):
+                buf = synth.normal_bf16(n * (seq + 1), synth.tensor_id(l, kind), c.seed, 1.0)[n * seq:]
+                dst[l] = buf.reshape(c.n_kv, cache_len, 64)[:, rows, :].copy()
 
     def step(self, token: int, pos: int, return_logits=False):
         c, w = self.c, self.w
@@ -171,13 +188,13 @@ class Model:
             a = attn_sink(q, self.k[l][:, lo:], self.v[l][:, lo:], ly["sinks"], c.n_kv).reshape(QD)
             h = (x + (ly["wo"].astype(np.float64) @ a.astype(np.float64)).astype(np.float32) + ly["bo"]).astype(np.float32)
             xn2 = rms_norm(ly["ln2"], h, c.eps)
-            guw, dnw = self._experts(l, ly)
             logits = mo.router_logits(xn2[None, :], ly["Wr"], ly["br"])
             idx, wt = mo.topk_softmax(logits, c.top_k)
             y = np.zeros(c.hidden, dtype=np.float32)
             for j in range(c.top_k):
                 e = int(idx[0, j])
-                o, _ = mo.expert_ffn(xn2, guw[e], ly["gu_bias"][e], dnw[e], ly["dn_bias"][e], c.alpha, c.limit)
+                guw, dnw = self._expert(l, ly, e)
+                o, _ = mo.expert_ffn(xn2, guw, ly["gu_bias"][e], dnw, ly["dn_bias"][e], c.alpha, c.limit)
                 y = (y + wt[0, j] * o).astype(np.float32)
             x = (h + y).astype(np.float32)
         xf = rms_norm(w["lnf"], x, c.eps)

@@ -151,6 +151,134 @@ def test_persistent_step_matches_per_op_step_at_full_width():
     a.close(), b.close()
 
 
+FULL_WIDTH = dict(layers=2, hidden=2880, inter=2880, experts=32, top_k=4, n_q=64, n_kv=8, vocab=4096, window=128,
+                  max_seq=2304, batch=1, seed=3)
+
+
+@pytest.mark.parametrize("flags", STEP_FLAGS)
+def test_full_width_steps_match_oracle_up_to_context_2048(flags):
+    """Two layers at the gpt-oss-20b widths (45-chunk MXFP4 rows, 152/160-row block-scaled instructions, 64 q / 8
+    kv heads, a 4096-wide o-proj input) against the C oracle: the first positions, then, on a synthetic KV cache
+    that both sides generate from the seed, positions around the first KV-slice boundaries and around 2048
+    (17 slices merged, the sliding layers' ring wrapped 16 times)."""
+    from oracle import c_oracle
+    c = GptOssConfig(**FULL_WIDTH, flags=flags)
+    m, o = GptOss(c), c_oracle.GptOssC(ocfg(c))
+    checked = 0
+
+    def step(tok, pos):
+        nonlocal checked
+        want, ref = o.step(tok, pos, return_logits=True)
+        got = int(m.infer([tok], [pos])[0])
+        logits = m.logits()[0]
+        assert rel(logits, ref) < TOL_LOGITS, f"pos {pos}: {rel(logits, ref)}"
+        top2 = np.sort(ref)[-2:]
+        if top2[1] - top2[0] > 4 * TOL_LOGITS * np.abs(ref).max():
+            assert got == want, f"pos {pos}"
+            checked += 1
+        return want
+
+    tok = 7
+    for pos in range(4):
+        tok = step(tok, pos)
+    m.fill_kv()
+    o.fill_kv()
+    for pos in (127, 128, 129, 255, 256, 257, 2046, 2047, 2048, 2049, 2200):
+        tok = step(tok, pos)
+    assert checked > 0
+    m.close(), o.close()
+
+
+@pytest.mark.parametrize("flags", STEP_FLAGS)
+def test_128_free_running_greedy_steps_match_oracle(flags):
+    """128 greedy steps with the argmax fed back on the device.  The oracle is fed the device's tokens and must
+    choose the same next token at every step whose top-2 margin exceeds twice the logit error bound; a second
+    instance replays the sequence step by step so that the bound itself is checked at every step."""
+    from oracle import c_oracle
+    GUARD = 1e-4
+    c = small(max_seq=160, flags=flags)
+    a, b, o = GptOss(c), GptOss(c), c_oracle.GptOssC(ocfg(c))
+    first = 11
+    a.prep([first], [0])
+    seq = a.decode(128)[:, 0].tolist()
+    tok, guarded, margins = first, 0, []
+    for pos in range(128):
+        want, ref = o.step(tok, pos, return_logits=True)
+        assert int(b.infer([tok], [pos])[0]) == seq[pos]
+        scale = float(np.abs(ref).max())
+        assert rel(b.logits()[0], ref) < GUARD, f"pos {pos}"
+        top2 = np.sort(ref)[-2:]
+        margins.append(float(top2[1] - top2[0]) / scale)
+        if margins[-1] > 2 * GUARD:
+            assert seq[pos] == want, f"pos {pos}: margin {margins[-1]:.2e}"
+            guarded += 1
+        tok = seq[pos]
+    print(f"top-2 margins / max|logit|: min {min(margins):.2e}, median {np.median(margins):.2e}; {guarded}/128 steps decided")
+    assert guarded >= 120
+    a.close(), b.close(), o.close()
+
+
+def test_steps_past_the_end_of_the_cache_are_refused():
+    c = small(max_seq=16)
+    m = GptOss(c)
+    m.prep([1], [13])
+    assert m.decode(2).shape == (2, 1)              # positions 13 and 14
+    assert m.decode(1).shape == (1, 1)              # position 15, the last one
+    with pytest.raises(RuntimeError, match="out of range"):
+        m.decode(1)
+    m.prep([1], [14])
+    with pytest.raises(RuntimeError, match="out of range"):
+        m.decode(3)
+    m.infer([1], [15])
+    with pytest.raises(RuntimeError, match="out of range"):
+        m.base.execute_into(m.art.extras["infer"], b"", bytearray(4))
+    m.close()
+
+
+def test_load_can_be_repeated_and_a_failed_load_leaves_no_memory_behind(monkeypatch):
+    import ctypes
+    from base_b200 import lib
+    L = lib()
+    probe = ctypes.c_void_p(0)
+    L.cl_cuda_init(ctypes.byref(probe))
+    c = small(layers=4)
+    m = GptOss(c)
+    t1 = int(m.infer([5], [0])[0])
+    m.base.execute(m.art.main, c.header())          # load again on a loaded instance
+    assert int(m.infer([5], [0])[0]) == t1
+    m.close()
+    free0 = L.cl_b200_mem_free(probe)
+    b = GptOss.__new__(GptOss)
+    from base_b200 import py_base
+    b.cfg, b.art = c, py_base.native_artifact("gptoss")
+    b.base = py_base.Base(b.art.setup)
+    monkeypatch.setenv("B200_TEST_FAIL_LOAD", "3")   # fails after three of the four layers are on the device
+    with pytest.raises(RuntimeError, match="failure requested"):
+        b.base.execute(b.art.main, c.header())
+    assert L.cl_b200_mem_free(probe) >= free0 - (1 << 20)
+    monkeypatch.delenv("B200_TEST_FAIL_LOAD")
+    b.base.execute(b.art.main, c.header())          # the same instance loads after the failure
+    assert int(b.infer([5], [0])[0]) == t1
+    b.close()
+    L.cl_cuda_cleanup(ctypes.byref(probe))
+
+
+@pytest.mark.parametrize("flags", STEP_FLAGS[1:])
+def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable(flags):
+    """The persistent kernel's producers leave out one ring fill (a test hook in the load header), so the
+    consumers' bounded wait for it gives up: the kernel stores a status code and ends, `infer` raises, and a
+    fresh instance on the same device decodes normally afterwards."""
+    c = small(layers=2, flags=flags, test_skip_fill=3, test_spin=20000)
+    m = GptOss(c)
+    with pytest.raises(RuntimeError, match="gave up waiting"):
+        m.infer([7], [0])
+    m.close()
+    ok = GptOss(small(layers=2, flags=flags))
+    ref = GptOss(small(layers=2, flags=PDL))
+    assert int(ok.infer([7], [0])[0]) == int(ref.infer([7], [0])[0])
+    ok.close(), ref.close()
+
+
 def test_persistent_step_needs_batch_one():
     with pytest.raises(RuntimeError, match="batch must be 1"):
         GptOss(small(batch=2, flags=PDL | PERSISTENT))
@@ -163,6 +291,4 @@ def test_bad_requests_are_reported():
         m.infer([c.vocab], [0])
     with pytest.raises(RuntimeError, match="out of range"):
         m.infer([1], [c.max_seq])
-    with pytest.raises(RuntimeError, match="already loaded"):
-        m.base.execute(m.art.main, c.header())
     m.close()

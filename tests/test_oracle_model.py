@@ -74,3 +74,88 @@ def test_tiny_model_runs_and_is_deterministic():
     t1 = [m1.step(3 + i, i) for i in range(6)]
     t2 = [m2.step(3 + i, i) for i in range(6)]
     assert t1 == t2 and all(0 <= t < 50 for t in t1)
+
+
+# ---- the C restatement of whole decode steps (oracle/model_oracle.c) against the NumPy oracles ----
+def _rel(a, b):
+    return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
+
+
+def test_c_gptoss_model_matches_numpy_model():
+    from oracle import c_oracle
+    c = go.Cfg(layers=3, hidden=128, inter=192, experts=8, top_k=4, n_q=8, n_kv=2, vocab=300, window=8, max_seq=40, seed=5)
+    a, b = go.Model(c), c_oracle.GptOssC(c, threads=2)
+    tok = 7
+    for pos in range(20):                                   # the sliding layers' ring (8 rows) wraps twice
+        ta, la = a.step(tok, pos, return_logits=True)
+        tb, lb = b.step(tok, pos, return_logits=True)
+        assert _rel(lb, la) < 2e-5, f"pos {pos}"
+        top2 = np.sort(la)[-2:]
+        if top2[1] - top2[0] > 1e-4 * np.abs(la).max():
+            assert ta == tb
+        tok = ta
+    st = b.stats()
+    assert st["experts"].shape == (3, 4) and st["moe_s"] > 0
+    b.close()
+
+
+def test_c_gptoss_synthetic_cache_matches_numpy_fill():
+    from oracle import c_oracle
+    c = go.Cfg(layers=2, hidden=128, inter=64, experts=4, top_k=2, n_q=4, n_kv=2, vocab=100, window=16, max_seq=300, seed=9)
+    a, b = go.Model(c), c_oracle.GptOssC(c, threads=2)
+    a.fill_kv(270)
+    b.fill_kv()
+    for pos, tok in ((270, 3), (271, 50)):
+        _, la = a.step(tok, pos, return_logits=True)
+        _, lb = b.step(tok, pos, return_logits=True)
+        assert _rel(lb, la) < 2e-5
+    # the filled rows matter: an empty cache gives different logits at the same position
+    e = go.Model(c)
+    e.k = [np.zeros((c.n_kv, 270, 64), dtype=np.float32) for _ in range(c.layers)]
+    e.v = [np.zeros((c.n_kv, 270, 64), dtype=np.float32) for _ in range(c.layers)]
+    _, le = e.step(3, 270, return_logits=True)
+    a2 = go.Model(c)
+    a2.fill_kv(270)
+    _, la2 = a2.step(3, 270, return_logits=True)
+    assert _rel(le, la2) > 1e-3
+    b.close()
+
+
+def test_c_qwen2_model_matches_numpy_model():
+    from oracle import c_oracle
+    from oracle import qwen2_oracle as qo
+    c = qo.Cfg(layers=2, hidden=128, inter=256, n_q=4, n_kv=2, vocab=400, max_seq=24, seed=3)
+    a, b = qo.Model(c), c_oracle.Qwen2C(c, threads=2)
+    tok = 11
+    for pos in range(12):
+        ta, la = a.step(tok, pos, return_logits=True)
+        tb, lb = b.step(tok, pos, return_logits=True)
+        assert _rel(lb, la) < 2e-5, f"pos {pos}"
+        top2 = np.sort(la)[-2:]
+        if top2[1] - top2[0] > 1e-4 * np.abs(la).max():
+            assert ta == tb
+        tok = ta
+    b.close()
+
+
+def test_rowdot_fold_is_the_reference_cpu_gemv_order():
+    # lean/algorithms/RowDotBenchAlgorithm.lean:86-121: four lane accumulators acc_j += x * w (separate
+    # multiply and add), (e0 + e1) + (e2 + e3), then a scalar tail; restated here in NumPy f32
+    from oracle import c_oracle
+    r = np.random.default_rng(4)
+    for K in (896, 2880, 2883):
+        W = r.standard_normal((5, K)).astype(np.float32)
+        x = r.standard_normal(K).astype(np.float32)
+        want = np.zeros(5, dtype=np.float32)
+        for i in range(5):
+            acc = np.zeros(4, dtype=np.float32)
+            n4 = K // 4 * 4
+            for j in range(0, n4, 4):
+                acc = (acc + (x[j:j + 4] * W[i, j:j + 4]).astype(np.float32)).astype(np.float32)
+            s = np.float32(np.float32(acc[0] + acc[1]) + np.float32(acc[2] + acc[3]))
+            for j in range(n4, K):
+                s = np.float32(s + np.float32(x[j] * W[i, j]))
+            want[i] = s
+        got = c_oracle.rowdot_gemv(W, x, threads=1)
+        np.testing.assert_array_equal(got.view(np.uint32), want.view(np.uint32))
+        np.testing.assert_array_equal(c_oracle.rowdot_gemv(W, x, threads=3).view(np.uint32), want.view(np.uint32))

@@ -126,3 +126,48 @@ def test_expert_range_needs_the_tensor_core_path():
     p = make_moe_params(cfg, seed=35)
     with pytest.raises(RuntimeError, match="expert range"):
         MoeFfn(cfg, p, max_tokens=8, flags=PDL, expert_lo=0, expert_n=4)
+
+
+def test_config_2_at_full_size_against_the_oracle():
+    """BASELINE config 2 as the bench runs it: 2048 tokens, hidden = inter = 2880 (45 K steps, 192-row tiles over
+    5760 and 2880 rows), 32 experts top-4, router skew 0.5 (uneven token counts).  Top-k indices and the token
+    permutation bit-exact for all 8192 assignments; outputs within 1e-2 on tokens of the least and the most
+    loaded expert, of the last (partial) token tile of the most loaded one, and a random sample."""
+    from oracle import c_oracle
+    cfg = MoeConfig()
+    assert (cfg.hidden, cfg.inter, cfg.experts, cfg.top_k) == (2880, 2880, 32, 4)
+    T = 2048
+    p = make_moe_params(cfg, seed=2000, skew=0.5)
+    x = bf16_exact(np.random.default_rng(2001).standard_normal((T, cfg.hidden)).astype(np.float32))
+    m = MoeFfn(cfg, p, max_tokens=T, flags=PDL | TENSOR_CORES)
+    y = m.forward(x)
+    idx, w = m.topk()
+    got = m.route()
+    m.close()
+    rlogits = mo.router_logits(x, p["Wr"], p["br"])
+    ridx, rw = mo.topk_softmax(rlogits, cfg.top_k)
+    safe = mo.topk_margin(rlogits, cfg.top_k) > 1e-5 * np.abs(rlogits).max()
+    assert safe.mean() > 0.99
+    np.testing.assert_array_equal(idx[safe], ridx[safe])
+    np.testing.assert_allclose(w[safe], rw[safe], atol=5e-6)
+    want = mo.route_tables(idx, cfg.experts)
+    for k in ("count", "offset", "active", "perm"):
+        np.testing.assert_array_equal(got[k], want[k], err_msg=k)
+    if safe.all():
+        ref_tables = mo.route_tables(ridx, cfg.experts)
+        for k in ("count", "offset", "active", "perm"):
+            np.testing.assert_array_equal(got[k], ref_tables[k], err_msg="oracle " + k)
+    count, offset, perm = want["count"], want["offset"], want["perm"]
+    assert count.max() > 2 * count.min()                   # the skew gives uneven loads
+    least, most = int(np.argmin(count)), int(np.argmax(count))
+    pick = []
+    for e, sl in ((least, slice(0, 4)), (most, slice(0, 4)), (most, slice(-4, None))):
+        pick += (perm[offset[e]:offset[e + 1]][sl] // cfg.top_k).tolist()
+    pick += np.random.default_rng(5).integers(0, T, size=12).tolist()
+    pick = np.array(sorted({t for t in pick if safe[t]}))
+    assert len(pick) >= 16 and np.isfinite(y).all()
+    ry, cidx, _ = c_oracle.moe_ffn(x[pick], p)
+    np.testing.assert_array_equal(cidx, idx[pick])
+    err = rel(y[pick], ry)
+    print(f"config 2 full size: tokens per expert {count.min()}..{count.max()}, max-rel-err {err:.2e} on {len(pick)} tokens")
+    assert err < TOL_BF16

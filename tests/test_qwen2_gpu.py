@@ -81,3 +81,51 @@ def test_one_step_at_qwen2_0_5b_shapes():
         assert rel(m.logits()[0], ref) < TOL
         tok = want
     m.close()
+
+
+def test_128_free_running_greedy_steps_at_config_1_widths():
+    """BASELINE config 1's protocol (32-token prompt, then 128 greedy tokens with the argmax fed back on the
+    device) at the Qwen2-0.5B widths with 4 of the 24 layers, against the C oracle fed the device's tokens: the
+    oracle must pick the same token wherever its top-2 margin exceeds twice the logit bound, and a second
+    instance replays the sequence step by step to check the bound itself at every step."""
+    from oracle import c_oracle
+    GUARD = 1e-4
+    c = Qwen2Config(layers=4, max_seq=176, seed=2)
+    a, b, o = Qwen2(c), Qwen2(c), c_oracle.Qwen2C(ocfg(c))
+    prompt = np.random.default_rng(1000).integers(0, c.vocab, size=32).tolist()
+    for pos in range(31):
+        a.infer([prompt[pos]], [pos])
+        b.infer([prompt[pos]], [pos])
+        o.step(prompt[pos], pos)
+    a.prep([prompt[31]], [31])
+    seq = a.decode(128)[:, 0].tolist()
+    tok, guarded, margins = prompt[31], 0, []
+    for i in range(128):
+        pos = 31 + i
+        want, ref = o.step(tok, pos, return_logits=True)
+        assert int(b.infer([tok], [pos])[0]) == seq[i]
+        assert rel(b.logits()[0], ref) < GUARD, f"pos {pos}"
+        top2 = np.sort(ref)[-2:]
+        margins.append(float(top2[1] - top2[0]) / float(np.abs(ref).max()))
+        if margins[-1] > 2 * GUARD:
+            assert seq[i] == want, f"pos {pos}: margin {margins[-1]:.2e}"
+            guarded += 1
+        tok = seq[i]
+    print(f"top-2 margins / max|logit|: min {min(margins):.2e}, median {np.median(margins):.2e}; {guarded}/128 steps decided")
+    assert guarded >= 110
+    a.close(), b.close(), o.close()
+
+
+def test_steps_past_the_end_of_the_cache_are_refused():
+    c = small(max_seq=16)
+    m = Qwen2(c)
+    m.prep([1], [14])
+    assert m.decode(2).shape == (2, 1)
+    with pytest.raises(RuntimeError, match="out of range"):
+        m.decode(1)
+    m.prep([1], [10])
+    with pytest.raises(RuntimeError, match="out of range"):
+        m.decode(7)
+    m.base.execute(m.art.main, c.header())       # load again on a loaded instance
+    assert m.infer([1], [0]).shape == (1,)
+    m.close()

@@ -186,3 +186,23 @@ def test_artifact_from_bincode_bytes():
 
 def test_run_helper():
     assert py_base.run(py_base.Setup("", 0, IO), py_base.Algorithm(0)) == []
+
+
+def test_huge_memory_size_and_deep_json_are_errors_not_corruption():
+    # memory_size near 2^64 must not wrap the allocation size; the reference aborts on such a resize
+    # (base/src/lib.rs:36-52), here it is an Execution error
+    for size in (2 ** 64 - 1, 2 ** 64 - 40, 2 ** 41):
+        with pytest.raises((RuntimeError, ValueError, OverflowError)):
+            py_base.Base(py_base.Setup("", size, IO))
+    art = py_base.native_artifact("moe_ffn")
+    d = json.loads(art.to_json())
+    d["setup"]["memory_size"] = 2 ** 64 - 1            # representable as u64: parsed exactly, refused by Base
+    a = py_base.loads_artifact(json.dumps(d))
+    assert a.setup.memory_size == 2 ** 64 - 1
+    with pytest.raises((RuntimeError, ValueError)):
+        py_base.Base(a.setup)
+    d["setup"]["memory_size"] = 2 ** 64                # not a u64
+    with pytest.raises(ValueError):
+        py_base.loads_artifact(json.dumps(d))
+    with pytest.raises(ValueError):
+        py_base.loads_artifact("[" * 100000 + "]" * 100000)

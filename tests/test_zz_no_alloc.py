@@ -68,3 +68,35 @@ def test_noalloc_argmax_matches_regular_entry_point_twice():
                                     ctypes.c_void_p(L.cl_b200_buffer_ptr(c, o2)), None) == -1
     assert b"exceed" in L.cl_b200_argmax_noalloc_error()
     L.cl_cuda_cleanup(ctypes.byref(slot))
+
+
+def test_noalloc_argmax_is_ordered_after_a_kernel_on_the_library_stream():
+    """The logits come from a kernel of this library on its main stream (a non-blocking stream, which the
+    default stream does not wait for); the argmax is given that stream's handle and nothing synchronises in
+    between, on two calls in a row.  A serving loop that may not allocate uses it exactly like this."""
+    L = lib()
+    slot = ctypes.c_void_p(0)
+    L.cl_cuda_init(ctypes.byref(slot))
+    assert slot.value, L.cl_b200_last_error().decode()
+    c = slot
+    mod = L.cl_b200_builtin_module(c)
+    handle = L.cl_b200_stream_handle(c, -1)
+    assert handle != 0 and L.cl_b200_stream_handle(c, 99) == 0
+    from oracle import synth
+    V, B = 150000, 4
+    lb = L.cl_cuda_create_buffer(c, B * V * 4)
+    ob = L.cl_cuda_create_buffer(c, B * 4)
+    for call, seed in enumerate((3, 4)):
+        # synth_fill, kind 2: f32 N(0, 1) values from (seed, tensor 77, index), generated on the main stream
+        args = struct.pack("<Q2Iif2i", B * V, 77, seed, 2, 1.0 / 209.0232, 0, 1)
+        bind = struct.pack("<i", lb)
+        assert L.cl_b200_launch(c, mod, b"synth_fill", 1, bind, args, len(args), 148 * 8, 1, 1, 256, 1, 1, 0, -1, 0) == 0
+        rc = L.cl_b200_argmax_noalloc(ctypes.c_void_p(L.cl_b200_buffer_ptr(c, lb)), V, B, V,
+                                      ctypes.c_void_p(L.cl_b200_buffer_ptr(c, ob)), ctypes.c_void_p(handle))
+        assert rc == 0, L.cl_b200_argmax_noalloc_error().decode()
+        assert L.cl_cuda_sync(c) == 0
+        got = np.zeros(B, dtype=np.int32)
+        assert L.cl_cuda_download_ptr(c, ob, got.ctypes.data_as(ctypes.c_void_p), got.nbytes) == 0
+        want = np.argmax(synth.normal(B * V, 77, seed, 1.0).reshape(B, V), axis=1)
+        np.testing.assert_array_equal(got, want, err_msg=f"call {call}")
+    L.cl_cuda_cleanup(ctypes.byref(slot))
