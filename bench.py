@@ -122,32 +122,104 @@ class ClockSampler:
                 "reasons": sorted(self.reasons)}
 
 
-def cpu_baseline(cfg, steps: int, full_threads: bool = True):
-    """The CPU port (C oracle, oracle/moe_oracle.c) on a bounded sample: ONE MoE
-    FFN layer of the workload (router, top-4, 4 experts' gate_up/SwiGLU/down,
-    combine), `steps` repetitions after one warm-up, median.  tokens/s is
-    extrapolated by bytes: a decode step streams step_bytes, the sample
-    streams one layer's expert + router bytes at the measured rate."""
-    from base_b200.moe import MoeConfig, make_moe_params, moe_layer_bytes
+def _ocfg(cfg, layers: int, max_seq: int):
+    from oracle import gptoss_oracle as go
+    return go.Cfg(layers=layers, hidden=cfg.hidden, inter=cfg.inter, experts=cfg.experts, top_k=cfg.top_k, n_q=cfg.n_q,
+                  n_kv=cfg.n_kv, vocab=cfg.vocab, window=cfg.window, max_seq=max_seq, batch=1,
+                  rope_theta=cfg.rope_theta, eps=cfg.eps, alpha=cfg.alpha, limit=cfg.limit, seed=cfg.seed)
+
+
+def host_threads() -> int:
+    """All host cores this process may use (torchrun exports OMP_NUM_THREADS=1; the C oracle is given the count)."""
+    return len(os.sched_getaffinity(0))
+
+
+def cpu_pieces(cfg, ctx: int, threads: int, reps: int = 3):
+    """Decode steps of a 2-layer model of the workload's widths (one sliding and one full-attention layer, the
+    whole vocabulary) on the C oracle, at context `ctx` on a synthetic KV cache: seconds per layer and for the
+    final norm + lm_head + argmax, measured per piece inside real steps (oracle/model_oracle.c keeps the split)."""
     from oracle import c_oracle
-    mc = MoeConfig(hidden=cfg.hidden, inter=cfg.inter, experts=cfg.experts, top_k=cfg.top_k)
-    p = make_moe_params(mc, seed=0)
-    x = np.random.default_rng(1).standard_normal((1, mc.hidden)).astype(np.float32)
-    # all host cores this process may use (torchrun exports OMP_NUM_THREADS=1, which the explicit count overrides)
-    threads = len(os.sched_getaffinity(0)) if full_threads else 1
-    c_oracle.moe_ffn(x, p, threads=threads)
-    ts = []
-    for _ in range(max(3, steps)):
+    o = c_oracle.GptOssC(_ocfg(cfg, 2, ctx + reps + 2), threads=threads)
+    o.fill_kv()
+    o.step(1, ctx)                                     # warm-up
+    s0 = o.stats()
+    for i in range(reps):
+        o.step(1 + i, ctx + 1 + i)
+    s1 = o.stats()
+    o.close()
+    layer_s = sum(s1[k] - s0[k] for k in ("dense_s", "attention_s", "moe_s")) / (2 * reps)
+    head_s = (s1["head_s"] - s0["head_s"]) / reps
+    return layer_s, head_s
+
+
+def cpu_baseline(cfg, ctx: int):
+    """The GPU arm's reported CPU baseline: the C port (oracle/model_oracle.c: the reference's RowDotBench GEMV
+    fold, its MX block dot, RMSNorm, RoPE, attention, argmax) on a bounded sample, a 2-layer model of the
+    workload's widths with the full vocabulary, timed on all host threads and on one (the reference's CPU GEMV is
+    single-threaded).  A whole step is composed from the measured pieces: layers x per-layer time + head time."""
+    threads = host_threads()
+    layer_all, head_all = cpu_pieces(cfg, ctx, threads, reps=3)
+    layer_1, head_1 = cpu_pieces(cfg, ctx, 1, reps=1)
+    step_all = cfg.layers * layer_all + head_all
+    step_1 = cfg.layers * layer_1 + head_1
+    return {"value": 1.0 / step_all, "unit": UNIT, "cores": threads, "kind": "port",
+            "one_core": {"value": 1.0 / step_1, "cores": 1, "ms_per_step": step_1 * 1e3},
+            "ms_per_step": step_all * 1e3, "nproc": os.cpu_count(),
+            "sample": f"real decode steps of a 2-layer model of the workload's widths (full vocabulary, context {ctx}, "
+                      f"synthetic KV cache): {layer_all * 1e3:.1f} ms per layer and {head_all * 1e3:.1f} ms for norm + "
+                      f"lm_head + argmax on {threads} threads ({layer_1 * 1e3:.0f} and {head_1 * 1e3:.0f} ms on one); "
+                      f"a step = {cfg.layers} x layer + head"}
+
+
+def cpu_reference(cfg, ctx: int, steps: int, warmup: int, budget_s: float = 150.0):
+    """The reference arm: REAL decode steps of the whole 24-layer workload on the C port, all host threads, at
+    context `ctx` on a synthetic KV cache (the 2048-token prompt is not replayed on the CPU).  Runs up to `steps`
+    timed steps after `warmup`, fewer when the time budget runs out (said in `sample`).  Falls back to composing
+    the step from measured pieces when the host cannot hold the 14 GB of weights."""
+    from oracle import c_oracle
+    threads = host_threads()
+    t_build = time.perf_counter()
+    try:
+        o = c_oracle.GptOssC(_ocfg(cfg, cfg.layers, ctx + steps + warmup + 2), threads=threads)
+    except MemoryError:
+        base = cpu_baseline(cfg, ctx)
+        base["sample"] = "host memory too small for the whole model; " + base["sample"]
+        return base, 1.0 / base["value"], 0
+    o.fill_kv()
+    t_build = time.perf_counter() - t_build
+    tok, pos, times = 1, ctx, []
+    t_start = time.perf_counter()
+    for i in range(warmup + steps):
         t0 = time.perf_counter()
-        c_oracle.moe_ffn(x, p, threads=threads)
-        ts.append(time.perf_counter() - t0)
-    t_layer = sorted(ts)[len(ts) // 2]
-    layer_bytes = moe_layer_bytes(mc)
-    t_step = t_layer * cfg.step_bytes(PROMPT) / layer_bytes
-    return {"value": 1.0 / t_step, "unit": UNIT, "cores": threads, "kind": "port",
-            "sample": f"one MoE FFN layer (hidden {mc.hidden}, 32 experts, top-4, 1 token) = {layer_bytes} B "
-                      f"in {t_layer * 1e3:.2f} ms median of {len(ts)}; scaled by bytes to a full decode step "
-                      f"({cfg.step_bytes(PROMPT)} B)"}, t_step
+        tok = o.step(tok, pos)
+        dt = time.perf_counter() - t0
+        pos += 1
+        if i >= min(warmup, 1):
+            times.append(dt)
+        if time.perf_counter() - t_start > budget_s and len(times) >= 2:
+            break
+    st = o.stats()
+    o.close()
+    layer_1, head_1 = cpu_pieces(cfg, ctx, 1, reps=1)
+    step_1 = cfg.layers * layer_1 + head_1
+    t_step = float(np.median(times))
+    total = st["dense_s"] + st["attention_s"] + st["moe_s"] + st["head_s"]
+    base = {"value": 1.0 / t_step, "unit": UNIT, "cores": threads, "kind": "port", "nproc": os.cpu_count(),
+            "ms_per_step": t_step * 1e3, "steps_timed": len(times),
+            "one_core": {"value": 1.0 / step_1, "cores": 1, "ms_per_step": step_1 * 1e3,
+                         "sample": "composed from a 2-layer model's measured per-layer and head times on one thread"},
+            "share": {k: round(st[k + "_s"] / total, 3) for k in ("dense", "attention", "moe", "head")},
+            "sample": f"{len(times)} real decode steps of the whole {cfg.layers}-layer model (weights generated from the "
+                      f"seed in {t_build:.0f} s, synthetic KV cache at context {ctx}), median {t_step * 1e3:.0f} ms, "
+                      f"min {min(times) * 1e3:.0f}, max {max(times) * 1e3:.0f}, on {threads} threads"}
+    return base, t_step, len(times)
+
+
+def f32_to_bf16_values(x: np.ndarray) -> np.ndarray:
+    """x rounded to bf16 (nearest even), as f32 values."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    r = ((u + np.uint64(0x7FFF) + ((u >> np.uint64(16)) & np.uint64(1))) >> np.uint64(16)).astype(np.uint32) << np.uint32(16)
+    return r.view(np.float32).reshape(x.shape)
 
 
 def run_qwen2(a, rank: int):
@@ -212,13 +284,12 @@ def run_prefill(a, rank: int):
     outputs (strong scaling: the work is fixed)."""
     from base_b200.dist import Ranks
     from base_b200.moe import MoeConfig, MoeFfn, MoeFfnEP, make_moe_params, PDL, TENSOR_CORES
-    from oracle import synth
     world = int(os.environ.get("WORLD_SIZE", "1"))
     T = 2048
     cfg = MoeConfig()
     p = make_moe_params(cfg, seed=2000, skew=0.5)
     x = np.random.default_rng(2001).standard_normal((T, cfg.hidden)).astype(np.float32)
-    x = (synth.f32_to_bf16_bits(x.reshape(-1)).astype(np.uint32) << 16).view(np.float32).reshape(T, cfg.hidden)
+    x = f32_to_bf16_values(x)
     A = T * cfg.top_k
     flops = A * 2.0 * (2 * cfg.inter + cfg.hidden) * cfg.hidden
     peak, kind = 1590.0, "fallback"
@@ -315,6 +386,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--prompt", type=int, default=PROMPT)
+    ap.add_argument("--repeats", type=int, default=5,
+                    help="how many times the K-step timed loop runs; the line reports the median repeat and the spread")
     ap.add_argument("--workload", choices=("gptoss", "qwen2", "prefill"), default="gptoss",
                     help="gptoss: BASELINE config 3 (the headline); qwen2: BASELINE config 1 (Qwen2-0.5B f32, single GPU); "
                          "prefill: BASELINE config 2 (one MoE layer, 2048 tokens, tensor cores)")
@@ -335,7 +408,7 @@ def main():
     from base_b200.gptoss import GPT_OSS_20B, GptOss, PDL, PERSISTENT, BLOCK_SCALED
     import dataclasses
     mx = a.step == "persistent" and a.experts == "block-scaled"
-    cfg = dataclasses.replace(GPT_OSS_20B, max_seq=a.prompt + a.warmup + 2 * a.steps + 8,
+    cfg = dataclasses.replace(GPT_OSS_20B, max_seq=a.prompt + a.warmup + (max(1, a.repeats) + 1) * a.steps + 8,
                               flags=PDL | (PERSISTENT if a.step == "persistent" else 0) | (BLOCK_SCALED if mx else 0))
     config = {"workload": "gpt-oss-20b decode, batch 1 per GPU, 2048-token prompt, greedy (BASELINE config 3)",
               "layers": cfg.layers, "hidden": cfg.hidden, "experts": cfg.experts, "top_k": cfg.top_k,
@@ -350,9 +423,12 @@ def main():
     if a.impl == "reference":
         if rank != 0:
             return
-        base, t_step = cpu_baseline(cfg, a.steps)
+        base, t_step, n_timed = cpu_reference(cfg, a.prompt, a.steps, a.warmup)
+        config = dict(config, step="C port of the reference's CPU path, one decode step per call",
+                      parallelism=f"{base['cores']} host threads")
+        config.pop("expert_phases", None)
         line = {"metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps,
-                "warmup": a.warmup, "ms_per_step": t_step * 1e3, "higher_is_better": True, "scaling": "weak",
+                "steps_timed": n_timed, "warmup": a.warmup, "ms_per_step": t_step * 1e3, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "mxfp4 weights, f32 accumulate", "data": "synthetic",
                 "config": config, "impl": "reference", "cpu_baseline": base,
                 "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -392,16 +468,25 @@ def main():
     sampler = ClockSampler(local)
     sampler.start()
     sampler.mark()
-    barrier()
-    m.prep([tok], [pos])
-    toks, ms = m.decode(a.steps, timed=True)
-    barrier()
-    ms = max_over_ranks(ms)
+    # the K-step loop, `repeats` times back to back (each continues where the last one stopped); every repeat
+    # is timed by device events and reduced to the max over ranks; the line reports the median repeat
+    rep_ms = []
+    for _ in range(max(1, a.repeats)):
+        barrier()
+        m.prep([tok], [pos])
+        toks, ms_r = m.decode(a.steps, timed=True)
+        barrier()
+        rep_ms.append(max_over_ranks(ms_r))
+        tok, pos = int(toks[-1, 0]), pos + a.steps
+    order = sorted(range(len(rep_ms)), key=lambda i: rep_ms[i])
+    mid = order[len(order) // 2]
+    ms = rep_ms[mid]
+    pos_mid = pos - (len(rep_ms) - mid) * a.steps       # where the median repeat started
     value = world * a.steps / (ms * 1e-3)
 
     # end to end: one execute_into per token, host buffers in and out
     # continues from where the device loop stopped
-    tok2, pos2 = int(toks[-1, 0]), pos + a.steps
+    tok2, pos2 = tok, pos
     barrier()
     t0 = time.perf_counter()
     seq = []
@@ -414,7 +499,7 @@ def main():
 
     peak, peak_kind = measured_peak_gbs()
     persistent = bool(cfg.flags & PERSISTENT)
-    step_bytes = cfg.step_bytes(pos)
+    step_bytes = cfg.step_bytes(pos_mid + a.steps // 2)
     step_s = ms * 1e-3 / a.steps
     gu_bytes, dn_bytes = cfg.gate_up_bytes(cfg.top_k), cfg.down_bytes(cfg.top_k)
     if persistent:
@@ -436,7 +521,7 @@ def main():
                 "expert_gemv": {"gate_up_gbs": gu_bytes / (gu_us * 1e-6) / 1e9, "gate_up_us": gu_us,
                                 "down_gbs": dn_bytes / (dn_us * 1e-6) / 1e9, "down_us": dn_us,
                                 "frac_of_peak": (gu_bytes + dn_bytes) / ((gu_us + dn_us) * 1e-6) / 1e9 / peak}}
-        launches = a.steps
+        launches = a.steps * len(rep_ms)
     else:
         # one launch per operation: the dominant kernel is the gate_up expert GEMV, timed alone
         # over all layers (distinct weights each launch, so nothing comes from L2)
@@ -451,17 +536,19 @@ def main():
                 "down_kernel": {"achieved": dn_bytes / (dn_ms * 1e-3 / (iters * cfg.layers)) / 1e9,
                                 "us_per_launch": dn_ms * 1e3 / (iters * cfg.layers)},
                 "whole_step": {"bytes": step_bytes, "achieved": step_bytes / step_s / 1e9}}
-        launches = a.steps * (1 + cfg.layers * 6 + 2)
+        launches = a.steps * len(rep_ms) * (1 + cfg.layers * 6 + 2)
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup,
             "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "mxfp4 experts / bf16 dense weights, f32 accumulate", "data": "synthetic",
             "config": config,
             "e2e": {"value": world * a.steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
-            "gpu_launches": launches, "clocks": clocks, "roofline": roof}
+            "gpu_launches": launches, "clocks": clocks, "roofline": roof,
+            "repeats": {"n": len(rep_ms), "ms_per_step": [round(r / a.steps, 5) for r in rep_ms],
+                        "reported": "median", "min_tokens_per_s": world * a.steps / (max(rep_ms) * 1e-3),
+                        "max_tokens_per_s": world * a.steps / (min(rep_ms) * 1e-3)}}
     m.close()
     if rank == 0:
-        base, _ = cpu_baseline(cfg, 5)
-        line["cpu_baseline"] = base
+        line["cpu_baseline"] = cpu_baseline(cfg, a.prompt)
         print(json.dumps(line))
     ranks.close()
 
