@@ -95,6 +95,11 @@ def lib() -> ctypes.CDLL:
     sig("cl_b200_sm_count", i32, vp)
     sig("cl_b200_mem_free", i64, vp)
     sig("cl_b200_stream_handle", i64, vp, i32)
+    sig("cl_b200_comm_unique_id", i32, vp)
+    sig("cl_b200_comm_init", i32, vp, vp, i32, i32)
+    sig("cl_b200_comm_world", i32, vp)
+    sig("cl_b200_comm_all_gather", i32, vp, i32, i64, i32, i64, i32)
+    sig("cl_b200_comm_all_to_all", i32, vp, i32, i32, i64, i32)
     sig("cl_b200_last_error", cp)
     sig("cl_b200_argmax_noalloc", i32, vp, i32, i32, i32, vp, vp)
     sig("cl_b200_argmax_noalloc_error", cp)

@@ -8,6 +8,7 @@
 // id leaves a tombstone so ids are never reused (cuda.rs:1222-1243).
 #include "b200abi.h"
 #include "cuda_dyn.h"
+#include "nccl_dyn.h"
 
 #include <cstdio>
 #include <cstdlib>
@@ -25,6 +26,7 @@ extern const unsigned char b200_kernels_image_end[];
 namespace {
 
 CudaDriver g_drv;
+NcclLib g_nccl;
 std::mutex g_drv_mu;
 thread_local std::string t_err;
 
@@ -68,6 +70,8 @@ struct B200CudaContext {
   std::vector<Module> modules;
   std::unordered_map<const void *, int> text_modules;  // PTX text address -> module id
   int builtin_module = -1;
+  ncclComm_t comm = nullptr;      // expert-parallel communicator (cl_b200_comm_init), else null
+  int comm_rank = 0, comm_world = 1;
 };
 
 namespace {
@@ -313,6 +317,7 @@ void cl_cuda_cleanup(B200CudaContext **slot) {
       for (auto &b : c->buffers) if (b.live) g_drv.p_cuMemFree(b.ptr);
       for (auto &p : c->pinned) if (p.live) g_drv.p_cuMemFreeHost(p.p);
       for (auto &m : c->modules) if (m.live) g_drv.p_cuModuleUnload(m.mod);
+      if (c->comm && g_nccl.ok) g_nccl.CommDestroy(c->comm);
       if (c->main_stream) g_drv.p_cuStreamDestroy(c->main_stream);
       g_drv.p_cuDevicePrimaryCtxRelease(c->dev);
     }
@@ -773,6 +778,81 @@ int64_t cl_b200_stream_handle(B200CudaContext *c, int32_t stream_id) {
   CUstream st = nullptr;
   if (!get_stream(c, stream_id, &st)) { set_err("stream_handle: bad stream id"); return 0; }
   return int64_t(reinterpret_cast<uintptr_t>(st));
+}
+
+// ---- collectives over NCCL (expert-parallel decode) --------------------------------------------
+int32_t cl_b200_comm_unique_id(uint8_t *out128) {
+  if (!out128) { set_err("comm_unique_id: null pointer"); return -1; }
+  std::lock_guard<std::mutex> g(g_drv_mu);
+  if (!g_nccl.load()) { set_err("libnccl.so.2 not available"); return -1; }
+  ncclUniqueId id;
+  const ncclResult_t r = g_nccl.GetUniqueId(&id);
+  if (r != 0) { set_err(std::string("ncclGetUniqueId: ") + g_nccl.GetErrorString(r)); return -1; }
+  memcpy(out128, id.internal, 128);
+  return 0;
+}
+
+int32_t cl_b200_comm_init(B200CudaContext *c, const uint8_t *id128, int32_t rank, int32_t world) {
+  if (!c) { set_err("null context"); return -1; }
+  if (!id128 || world < 1 || rank < 0 || rank >= world) { set_err("comm_init: bad arguments"); return -1; }
+  {
+    std::lock_guard<std::mutex> g(g_drv_mu);
+    if (!g_nccl.load()) { set_err("libnccl.so.2 not available"); return -1; }
+  }
+  std::lock_guard<std::mutex> g(c->mu);
+  if (!bind(c)) return -1;
+  if (c->comm) { set_err("comm_init: already initialised"); return -1; }
+  ncclUniqueId id;
+  memcpy(id.internal, id128, 128);
+  const ncclResult_t r = g_nccl.CommInitRank(&c->comm, world, id, rank);
+  if (r != 0) { c->comm = nullptr; set_err(std::string("ncclCommInitRank: ") + g_nccl.GetErrorString(r)); return -1; }
+  c->comm_rank = rank;
+  c->comm_world = world;
+  return 0;
+}
+
+int32_t cl_b200_comm_world(B200CudaContext *c) { return c && c->comm ? c->comm_world : 1; }
+
+// recv[r * bytes .. (r + 1) * bytes) on every rank = rank r's send[send_offset .. + bytes).
+int32_t cl_b200_comm_all_gather(B200CudaContext *c, int32_t send_buf, int64_t send_offset, int32_t recv_buf, int64_t bytes,
+                                int32_t stream_id) {
+  if (!c) { set_err("null context"); return -1; }
+  std::lock_guard<std::mutex> g(c->mu);
+  if (!bind(c)) return -1;
+  if (!c->comm) { set_err("all_gather: no communicator"); return -1; }
+  Buffer *s = get_buf(c, send_buf), *d = get_buf(c, recv_buf);
+  CUstream st;
+  if (!s || !d || bytes <= 0 || send_offset < 0 || send_offset + bytes > s->size || bytes * c->comm_world > d->size ||
+      !get_stream(c, stream_id, &st)) {
+    set_err("all_gather: bad buffer, size or stream");
+    return -1;
+  }
+  const ncclResult_t r = g_nccl.AllGather(reinterpret_cast<const void *>(s->ptr + send_offset), reinterpret_cast<void *>(d->ptr),
+                                          size_t(bytes), kNcclUint8, c->comm, st);
+  if (r != 0) { set_err(std::string("ncclAllGather: ") + g_nccl.GetErrorString(r)); return -1; }
+  return 0;
+}
+
+// Rank r receives send[r * bytes .. + bytes) of every rank q into recv[q * bytes .. + bytes) (grouped send/recv).
+int32_t cl_b200_comm_all_to_all(B200CudaContext *c, int32_t send_buf, int32_t recv_buf, int64_t bytes, int32_t stream_id) {
+  if (!c) { set_err("null context"); return -1; }
+  std::lock_guard<std::mutex> g(c->mu);
+  if (!bind(c)) return -1;
+  if (!c->comm) { set_err("all_to_all: no communicator"); return -1; }
+  Buffer *s = get_buf(c, send_buf), *d = get_buf(c, recv_buf);
+  CUstream st;
+  if (!s || !d || bytes <= 0 || bytes * c->comm_world > s->size || bytes * c->comm_world > d->size || !get_stream(c, stream_id, &st)) {
+    set_err("all_to_all: bad buffer, size or stream");
+    return -1;
+  }
+  ncclResult_t r = g_nccl.GroupStart();
+  for (int q = 0; q < c->comm_world && r == 0; ++q) {
+    r = g_nccl.Send(reinterpret_cast<const void *>(s->ptr + size_t(q) * bytes), size_t(bytes), kNcclUint8, q, c->comm, st);
+    if (r == 0) r = g_nccl.Recv(reinterpret_cast<void *>(d->ptr + size_t(q) * bytes), size_t(bytes), kNcclUint8, q, c->comm, st);
+  }
+  const ncclResult_t r2 = g_nccl.GroupEnd();
+  if (r != 0 || r2 != 0) { set_err(std::string("all_to_all: ") + g_nccl.GetErrorString(r != 0 ? r : r2)); return -1; }
+  return 0;
 }
 
 int64_t cl_b200_mem_free(B200CudaContext *c) {

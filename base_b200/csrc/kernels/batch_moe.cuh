@@ -1,0 +1,367 @@
+// MXFP4 expert GEMVs for a BATCH of tokens on the block-scaled tensor cores (tcgen05.mma.kind::mxf4): every
+// expert's weights are read once for all the tokens routed to it.
+//
+// Same arithmetic as the one-token path (moe_mx.cuh, the expert phases of mega_decode.cuh): the weights are the
+// B operand as stored (codes + UE8M0 scales, "wide" layout of mxfp4_retile_wide with 8 K blocks per chunk), the
+// activations are the A operand written in balanced radix 8 (mx_expand_radix8: 8 E2M1 digit rows per token with
+// block scales 8^(7-t), exact to 2^-22 of each 32-element block's maximum), y = sum of the 8 digit rows.  Here a
+// token takes 8 of the 128 A rows, so ONE instruction serves up to 16 tokens of an expert; an expert with more
+// tokens is run in passes of 16 (its weights are then served from L2).
+//
+//   moe_expand_digits   f32 rows -> digits, in the order of the routing permutation (an expert's tokens contiguous):
+//                       dig [K block][position][8 digit rows x 16 B], em [position][96] block exponents
+//   moe_batch_mx_*      units = (expert, pass of <= 16 tokens, segment of <= 16 eight-row groups): N <= 128 rows per
+//                       instruction; producer warp (bulk copies: the segment's codes + scale words and the tokens'
+//                       digits of one chunk per ring slot), scale warp (weights' scale words -> tensor memory), issuer,
+//                       four epilogue warps (each reads the accumulator rows of four tokens, adds the digit rows,
+//                       bias, clamped SwiGLU).
+// Routing tables are those of moe_route_tables_many (count / offset / perm).  Every wait is bounded.
+#pragma once
+#include "moe_mx.cuh"
+
+constexpr int kBmTok = 16;                   // tokens per pass
+constexpr int kBmGroups = 16;                // 8-row groups per unit (N = 128)
+constexpr int kBmKc = 8;                     // K blocks per chunk
+constexpr int kBmSlots = 5;
+constexpr int kBmBBytes = kBmGroups * (kBmKc * 128 + 64);      // 17408: codes + scale words of a chunk
+constexpr int kBmABytes = kBmKc * kBmTok * 128;                // 16384: digits of a chunk
+constexpr int kBmSlotBytes = kBmBBytes + kBmABytes;
+constexpr int kBmThreads = 224;              // warps 0..3 epilogue, 4 scale words, 5 issuer, 6 producer
+constexpr int kBmEmStride = 96;
+constexpr int kBmMaxUnits = 192;             // units one CTA can take
+
+// ---- activations -> digits -----------------------------------------------------------------------------
+// grid = positions [pos0, pos0 + n) of the permutation, 384 threads (4 per K block).  Position p holds assignment
+// a = perm[p]; its source row is x[a / top_k] (gate_up: the token's normalised hidden state) or x[a] (down: the
+// assignment's activation).  P = total positions (the stride of the digit array).
+struct ExpandArgs { int K, P, pos0, n, top_k, per_token, E; };
+
+extern "C" __global__ void __launch_bounds__(384)
+moe_expand_digits(const float *__restrict__ x, const int *__restrict__ route, uint8_t *__restrict__ dig,
+                  uint8_t *__restrict__ em, ExpandArgs a) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int E = a.E;
+  const int *perm = route + 1 + E + (E + 1) + E;
+  const int *offset = route + 1 + E;
+  // pos0 < 0: the range is the one of experts [-pos0 - 1, -pos0 - 1 + n) (read from the tables on the device)
+  int p0 = a.pos0, cnt = a.n;
+  if (a.pos0 < 0) { const int lo = -a.pos0 - 1; p0 = offset[lo]; cnt = offset[lo + a.n] - p0; }
+  const int kblocks = a.K >> 5;
+  for (int pi = blockIdx.x; pi < cnt; pi += gridDim.x) {
+    const int p = p0 + pi, asg = perm[p];
+    const float *src = x + size_t(a.per_token ? asg / a.top_k : asg) * a.K;
+    const int kb = threadIdx.x >> 2, sub = threadIdx.x & 3;
+    const bool valid = kb < kblocks;
+    float v[8];
+    const float4 v0 = valid ? __ldcg(reinterpret_cast<const float4 *>(src + kb * 32 + sub * 8)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 v1 = valid ? __ldcg(reinterpret_cast<const float4 *>(src + kb * 32 + sub * 8 + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    v[0] = v0.x; v[1] = v0.y; v[2] = v0.z; v[3] = v0.w; v[4] = v1.x; v[5] = v1.y; v[6] = v1.z; v[7] = v1.w;
+    float m = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[i]));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+    uint32_t e8 = (__float_as_uint(m) >> 23) & 0xffu;
+    int X[8];
+    if (e8 >= 40 && e8 < 255) {
+      const float up = __uint_as_float((275u - e8) << 23);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) X[i] = __float2int_rn(v[i] * up);
+    } else {
+      e8 = 40;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) X[i] = 0;
+    }
+    if (valid) {
+      uint8_t *d = dig + (size_t(kb) * a.P + p) * 128 + sub * 4;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {                       // digit q (weight 8^q) is digit row 7 - q
+        uint32_t word = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int t1 = X[i] + 4;
+          word |= ((kMxDigitLut >> ((t1 & 7) << 2)) & 15u) << (4 * i);
+          X[i] = t1 >> 3;
+        }
+        *reinterpret_cast<uint32_t *>(d + (7 - q) * 16) = word;
+      }
+      if (sub == 0) em[size_t(p) * kBmEmStride + kb] = uint8_t(e8);
+    }
+    // K blocks past the end of the row (padding of the last 4-block group): exponent 127
+    if (threadIdx.x < kBmEmStride - kblocks) em[size_t(p) * kBmEmStride + kblocks + threadIdx.x] = 127;
+  }
+}
+
+// ---- the expert kernel -----------------------------------------------------------------------------------
+struct BatchMxArgs {
+  MoeDims d;
+  int lo, n;            // experts [lo, lo + n) are resident here; the weight array starts at expert lo, the biases at expert 0
+  int P;                // positions of the digit array (all assignments of the step)
+};
+
+struct BmUnit { int16_t e, pass, g0, ng; };
+
+struct BmBars {
+  uint64_t full[kBmSlots], empty[kBmSlots], sready[kBmSlots], done, uready;
+  uint32_t tmem_base;
+  int abort, n_units, u_base;
+};
+
+B200_DEVICE bool bm_wait(uint64_t *bar, uint32_t parity, BmBars *b, int *status, int code) {
+  const uint32_t lim = *reinterpret_cast<volatile int *>(&b->abort) ? 4096u : kTcSpin;
+  for (uint32_t i = 0; i < lim; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  *reinterpret_cast<volatile int *>(&b->abort) = 1;
+  atomicCAS(status, 0, code);
+  return false;
+}
+
+B200_DEVICE int bm_smem_bytes() { return kBmSlots * kBmSlotBytes + kBmMaxUnits * int(sizeof(BmUnit)) + int(sizeof(BmBars)) + 64; }
+
+// Two instructions over four consecutive K blocks (scale bytes 0,1 then 2,3 of one column group), issued by an
+// elected lane of the converged warp; the second one's operands are a_step / b_step descriptor units further.
+B200_DEVICE void bm_mma_pair_warp(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc01, uint32_t idesc23,
+                                  uint32_t sfa_tmem, uint32_t sfb_tmem, bool accumulate_first, bool second, uint32_t a_step,
+                                  uint32_t b_step) {
+  asm volatile(
+      "{\n.reg .pred p, q, e, e2;\n.reg .b64 a2, b2, sa, sb;\n"
+      "elect.sync _|e, 0xffffffff;\n"
+      "setp.ne.b32 p, %5, 0;\nsetp.eq.b32 q, %5, %5;\nsetp.ne.b32 e2, %8, 0;\nand.pred e2, e2, e;\n"
+      "@e tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%6], [%7], p;\n"
+      "cvt.u64.u32 sa, %9;\ncvt.u64.u32 sb, %10;\nadd.u64 a2, %1, sa;\nadd.u64 b2, %2, sb;\n"
+      "@e2 tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], a2, b2, %4, [%6], [%7], q;\n}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc01), "r"(idesc23), "r"(uint32_t(accumulate_first)), "r"(sfa_tmem), "r"(sfb_tmem),
+      "r"(uint32_t(second)), "r"(a_step), "r"(b_step)
+      : "memory");
+}
+
+// Four words per lane -> four consecutive columns.
+B200_DEVICE void tc_st_cols4(uint32_t taddr, uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {      // whole warp
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(w0), "r"(w1), "r"(w2), "r"(w3)
+               : "memory");
+}
+
+template <bool GATE_UP>
+B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__restrict__ bias, const uint8_t *__restrict__ dig,
+                               const uint8_t *__restrict__ em, const int *__restrict__ route, float *__restrict__ out,
+                               int *__restrict__ status, const BatchMxArgs &a) {
+  const MoeDims &d = a.d;
+  const int K = GATE_UP ? d.H : d.I, R = GATE_UP ? 2 * d.I : d.H, E = d.E;
+  const int kblocks = K >> 5, nch = (kblocks + kBmKc - 1) / kBmKc, G = R >> 3, nseg = (G + kBmGroups - 1) / kBmGroups;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint8_t *ring = dyn_smem;
+  BmUnit *units = reinterpret_cast<BmUnit *>(dyn_smem + kBmSlots * kBmSlotBytes);
+  BmBars *bars = reinterpret_cast<BmBars *>(dyn_smem + kBmSlots * kBmSlotBytes + kBmMaxUnits * sizeof(BmUnit));
+  const int *count = route + 1, *offset = route + 1 + E, *perm = route + 1 + E + (E + 1) + E;
+
+  if (tid == 0) {
+    for (int i = 0; i < kBmSlots; ++i) { mbar_init(&bars->full[i], 1); mbar_init(&bars->empty[i], 1); mbar_init(&bars->sready[i], 1); }
+    mbar_init(&bars->done, 1);
+    mbar_init(&bars->uready, 4);
+    bars->abort = 0;
+  }
+  fence_barrier_init();
+  if (warp == 0) tc_alloc(&bars->tmem_base, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = bars->tmem_base;
+  const uint32_t tSFA = tmem, tSFB = tmem + 96, tD = tmem + 192;
+  pdl_wait();
+  pdl_launch_dependents();
+
+  // ---- this CTA's units: all (expert, segment, pass) triples in that order, cut evenly over the grid
+  if (tid == 0) {
+    int total = 0;
+    for (int e = a.lo; e < a.lo + a.n; ++e) total += ((count[e] + kBmTok - 1) / kBmTok) * nseg;
+    const int u0 = int((long long)total * blockIdx.x / gridDim.x), u1 = int((long long)total * (blockIdx.x + 1) / gridDim.x);
+    bars->u_base = u0;
+    bars->n_units = u1 - u0;
+    if (u1 - u0 > kBmMaxUnits) { bars->n_units = 0; atomicCAS(status, 0, 71); }
+  }
+  __syncthreads();
+  const int n_units = bars->n_units;
+  for (int i = tid; i < n_units; i += kBmThreads) {
+    int idx = bars->u_base + i, e = a.lo;
+    for (; e < a.lo + a.n; ++e) {
+      const int ue = ((count[e] + kBmTok - 1) / kBmTok) * nseg;
+      if (idx < ue) break;
+      idx -= ue;
+    }
+    const int passes = (count[min(e, a.lo + a.n - 1)] + kBmTok - 1) / kBmTok;
+    const int seg = idx / max(passes, 1), pass = idx % max(passes, 1);
+    BmUnit u;
+    u.e = int16_t(e); u.pass = int16_t(pass); u.g0 = int16_t(seg * kBmGroups); u.ng = int16_t(min(kBmGroups, G - seg * kBmGroups));
+    units[i] = u;
+  }
+  __syncthreads();
+  const size_t mbytes = mxw_matrix_bytes(kblocks, kBmKc, R);
+
+  if (warp == 6) {
+    // ---- producer
+    if (lane == 0) {
+      uint32_t q = 0;
+      for (int ui = 0; ui < n_units; ++ui) {
+        const BmUnit u = units[ui];
+        const int off = offset[u.e] + u.pass * kBmTok, nt = min(kBmTok, count[u.e] - u.pass * kBmTok);
+        const uint8_t *wexp = W + size_t(u.e - a.lo) * mbytes;
+        for (int c = 0; c < nch; ++c, ++q) {
+          const uint32_t s = q % kBmSlots;
+          if (q >= kBmSlots && !bm_wait(&bars->empty[s], ((q / kBmSlots) - 1) & 1, bars, status, 72)) { ui = n_units; break; }
+          const int kcc = min(kBmKc, kblocks - c * kBmKc), gb = mxw_group_bytes(kcc);
+          uint8_t *dst = ring + size_t(s) * kBmSlotBytes;
+          mbar_expect_tx(&bars->full[s], uint32_t(u.ng * gb + kcc * nt * 128));
+          bulk_g2s(dst, wexp + mxw_chunk_base(c, kBmKc, R) + size_t(u.g0) * gb, uint32_t(u.ng * gb), &bars->full[s]);
+          for (int kbl = 0; kbl < kcc; ++kbl)
+            bulk_g2s(dst + kBmBBytes + kbl * (kBmTok * 128), dig + (size_t(c * kBmKc + kbl) * a.P + off) * 128, uint32_t(nt * 128),
+                     &bars->full[s]);
+        }
+      }
+    }
+  } else if (warp == 4) {
+    // ---- weights' scale words -> tensor memory (this warp shares warp 0's tensor-memory lanes), per ring slot
+    uint32_t q = 0;
+    for (int ui = 0; ui < n_units; ++ui) {
+      const BmUnit u = units[ui];
+      const int N = u.ng * 8;
+      bool ok = true;
+      for (int c = 0; c < nch && ok; ++c, ++q) {
+        const uint32_t s = q % kBmSlots;
+        ok = bm_wait(&bars->full[s], (q / kBmSlots) & 1, bars, status, 73);
+        if (!ok) break;
+        const int kcc = min(kBmKc, kblocks - c * kBmKc), gb = mxw_group_bytes(kcc);
+        const uint8_t *sw = ring + size_t(s) * kBmSlotBytes + size_t(lane >> 3) * gb + kcc * 128 + (lane & 7) * 4;
+        for (int j = 0; j < (kcc + 3) / 4; ++j) {
+          uint32_t w[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            w[i] = (i < 4 && lane + 32 * i < N) ? *reinterpret_cast<const uint32_t *>(sw + size_t(4 * i) * gb + j * 32) : 0u;
+          tc_st_words8(tSFB + s * 16 + j * 8, w);
+        }
+        tc_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->sready[s]);
+      }
+      if (!ok) break;
+    }
+  } else if (warp == 5) {
+    // ---- issuer (whole warp, an elected lane issues)
+    uint32_t q = 0;
+    for (int ui = 0; ui < n_units; ++ui) {
+      const BmUnit u = units[ui];
+      const int N = u.ng * 8;
+      if (!bm_wait(&bars->uready, ui & 1, bars, status, 74)) break;      // the tokens' scales are in place, the accumulator is free
+      tc_fence_after_sync();
+      const uint32_t id0 = mx_idesc(128, N, 0, 0), id2 = mx_idesc(128, N, 2, 2);
+      bool ok = true;
+      for (int c = 0; c < nch && ok; ++c, ++q) {
+        const uint32_t s = q % kBmSlots;
+        ok = bm_wait(&bars->sready[s], (q / kBmSlots) & 1, bars, status, 75);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const int kcc = min(kBmKc, kblocks - c * kBmKc), gb = mxw_group_bytes(kcc);
+        const uint32_t sb = smem_u32(ring + size_t(s) * kBmSlotBytes), sa = sb + kBmBBytes;
+        for (int pp = 0; 4 * pp < kcc; ++pp) {
+          const uint64_t da = tc_smem_desc(sa + uint32_t(4 * pp) * (kBmTok * 128), kBmTok * 128, 128);
+          const uint64_t db = tc_smem_desc(sb + uint32_t(4 * pp) * 128, 128, uint32_t(gb));
+          bm_mma_pair_warp(tD, da, db, id0, id2, tSFA + 4 * uint32_t(c * (kBmKc >> 2) + pp), tSFB + s * 16 + uint32_t(pp) * 8,
+                           !(c == 0 && pp == 0), 4 * pp + 2 < kcc, uint32_t(2 * kBmTok * 128) >> 4, 256u >> 4);
+        }
+        tc_commit_warp(&bars->empty[s], true);
+        tc_commit_warp(&bars->done, c == nch - 1);
+        __syncwarp();
+      }
+      if (!ok) break;
+    }
+  } else if (warp < 4) {
+    // ---- tokens' scales (warp 0) and the epilogue
+    for (int ui = 0; ui < n_units; ++ui) {
+      const BmUnit u = units[ui];
+      const int N = u.ng * 8;
+      const int off = offset[u.e] + u.pass * kBmTok, nt = min(kBmTok, count[u.e] - u.pass * kBmTok);
+      if (warp == 0) {
+        // row 32 q + lane of A = digit row (lane & 7) of token 4 q + (lane >> 3); scale byte = exponent - 21 + 3 (7 - digit row)
+        const uint32_t adj = 0x01010101u * uint32_t(3 * (7 - (lane & 7)));
+        for (int gg = 0; gg < (kblocks + 3) / 4; ++gg) {
+          uint32_t w[4];
+#pragma unroll
+          for (int qd = 0; qd < 4; ++qd) {
+            const int t = 4 * qd + (lane >> 3);
+            w[qd] = t < nt ? __ldcg(reinterpret_cast<const uint32_t *>(em + size_t(off + t) * kBmEmStride) + gg) + adj - 0x15151515u
+                           : 0x7f7f7f7fu;
+          }
+          tc_st_cols4(tSFA + 4 * gg, w[0], w[1], w[2], w[3]);
+        }
+        tc_wait_st();
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->uready);
+      if (!bm_wait(&bars->done, ui & 1, bars, status, 76)) break;
+      tc_fence_after_sync();
+      const int tt = 4 * warp + (lane >> 3);
+      const int asg = tt < nt ? perm[off + tt] : 0;
+      for (int c0 = 0; c0 < N; c0 += 32) {
+        float v[32];
+        {
+          float lo16[16], hi16[16];
+          tc_ld16(tD + (uint32_t(warp * 32) << 16) + uint32_t(c0), lo16);
+          tc_ld16(tD + (uint32_t(warp * 32) << 16) + uint32_t(c0 + 16), hi16);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) { v[i] = lo16[i]; v[16 + i] = hi16[i]; }
+        }
+        float r16[16], r8[8], r4[4];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float mine = (lane & 4) ? v[16 + i] : v[i], other = (lane & 4) ? v[i] : v[16 + i];
+          r16[i] = mine + __shfl_xor_sync(0xffffffffu, other, 4);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float mine = (lane & 2) ? r16[8 + i] : r16[i], other = (lane & 2) ? r16[i] : r16[8 + i];
+          r8[i] = mine + __shfl_xor_sync(0xffffffffu, other, 2);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float mine = (lane & 1) ? r8[4 + i] : r8[i], other = (lane & 1) ? r8[i] : r8[4 + i];
+          r4[i] = mine + __shfl_xor_sync(0xffffffffu, other, 1);
+        }
+        const int col = c0 + 4 * (lane & 7);
+        if (tt < nt && col < N) {
+          const int row = u.g0 * 8 + col;
+          const float4 b = __ldg(reinterpret_cast<const float4 *>(bias + size_t(u.e) * R + row));
+          if (GATE_UP) {
+            *reinterpret_cast<float2 *>(out + size_t(asg) * (R >> 1) + (row >> 1)) =
+                make_float2(swiglu_clamped(r4[0] + b.x, r4[1] + b.y, d.alpha, d.limit),
+                            swiglu_clamped(r4[2] + b.z, r4[3] + b.w, d.alpha, d.limit));
+          } else {
+            *reinterpret_cast<float4 *>(out + size_t(asg) * R + row) = make_float4(r4[0] + b.x, r4[1] + b.y, r4[2] + b.z, r4[3] + b.w);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tc_dealloc(tmem, 512);
+  }
+}
+
+// grid = one CTA per SM (any number works), kBmThreads threads, dynamic shared memory bm_smem_bytes().
+extern "C" __global__ void __launch_bounds__(kBmThreads, 1)
+moe_batch_mx_gate_up(const uint8_t *__restrict__ W, const float *__restrict__ bias, const uint8_t *__restrict__ dig,
+                     const uint8_t *__restrict__ em, const int *__restrict__ route, float *__restrict__ act,
+                     int *__restrict__ status, BatchMxArgs a) {
+  batch_mx_body<true>(W, bias, dig, em, route, act, status, a);
+}
+
+extern "C" __global__ void __launch_bounds__(kBmThreads, 1)
+moe_batch_mx_down(const uint8_t *__restrict__ W, const float *__restrict__ bias, const uint8_t *__restrict__ dig,
+                  const uint8_t *__restrict__ em, const int *__restrict__ route, float *__restrict__ o,
+                  int *__restrict__ status, BatchMxArgs a) {
+  batch_mx_body<false>(W, bias, dig, em, route, o, status, a);
+}

@@ -34,13 +34,14 @@ struct SynthArgs {
   int kind;               // 0 bytes, 1 scales, 2 normal f32, 3 normal bf16, 4 f32 1 + normal
   float c;                // sigma / 209.0232 for the normal kinds
   int lo, span;           // scales
+  unsigned long long first;   // index of element 0 of dst within the tensor (a slice of a larger tensor)
 };
 
 extern "C" __global__ void __launch_bounds__(256)
 synth_fill(void *__restrict__ dst, SynthArgs a) {
   const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
   for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += stride) {
-    const uint32_t i32 = uint32_t(i);
+    const uint32_t i32 = uint32_t(a.first + i);
     switch (a.kind) {
       case 0: {
         const uint32_t h = synth_hash(i32 >> 2, a.tensor, a.seed);

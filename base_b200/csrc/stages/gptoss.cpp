@@ -41,12 +41,18 @@ struct GptOssHeader {
   uint32_t flags;        // bit 0: programmatic dependent launch; bit 2: one f16 column per token in the experts;
                          // bit 5: the whole step as one persistent kernel (batch 1)
                          // bit 6: with bit 5, the experts run on the block-scaled tensor cores (mx tiles, moe_mx.cuh)
+                         // bit 7: batched mode (up to 256 sequences per GPU): dense layers and experts on the tcgen05
+                         //        tensor cores, weights read once per step for all sequences (batch_dense.cuh, batch_moe.cuh)
   uint32_t expert_lo, expert_n;   // experts resident on this rank (expert_n = 0: all)
   // Failure-path test hooks of the persistent step kernel (0 in production): 1 + the ring fill its producers
   // leave out, and the iteration limit of its waits (0: the default).  With a fill left out the consumers'
   // bounded wait runs out, the kernel stores a status code and ends, and `infer` reports it.
   uint32_t test_skip_fill, test_spin;
-  uint32_t reserved[9];
+  // Batched mode (flags bit 7) over several GPUs: this process is rank ep_rank of ep_world (0 or 1: one GPU).
+  // It holds `batch` of the ep_world * batch sequences (their KV caches; dense weights are replicated) and the
+  // experts [ep_rank * experts / ep_world, ...) of every layer.
+  uint32_t ep_rank, ep_world;
+  uint32_t reserved[7];
 };
 static_assert(sizeof(GptOssHeader) == 128, "header is 128 bytes");
 constexpr uint32_t kMagic = 0x31534f47;  // "GOS1"
@@ -77,7 +83,17 @@ constexpr int kMegaThreads = 512;
 constexpr int kMegaSmemBytes = 7 * 25088 + 56832;   // ring + MegaSmem (mega_decode.cuh): all 227 KB
 constexpr int kMxSlotBytes = 25088;
 struct RetileWideArgs { int R, K, n_mat, kc; };
-struct SynthArgs { unsigned long long n; uint32_t tensor, seed; int kind; float c; int lo, span; };
+struct DenseRetileArgs { int rows, K; };
+struct RowsToAArgs { int K, B, mode, n_parts; long long part_stride; float eps; };
+struct DenseTcArgs { int rows, K, B, kind, m64_rows16, out_stride; };
+struct ExpandArgs { int K, P, pos0, n, top_k, per_token, E; };
+struct BatchMxArgs { MoeDims d; int lo, n, P; };
+struct RouterManyArgs { int T, H, E; };
+struct TablesManyArgs { int A, E, lo, n; };
+struct CombineRangeArgs { int H, top_k, lo, n; };
+constexpr int kBdThreads = 192, kBdSmemBytes = 6 * (8192 + 16 * 1024) + 64 * 129 * 4 + 256;
+constexpr int kBmThreads = 224, kBmSmemBytes = 5 * (16 * (8 * 128 + 64) + 8 * 16 * 128) + 192 * 8 + 256;
+struct SynthArgs { unsigned long long n; uint32_t tensor, seed; int kind; float c; int lo, span; unsigned long long first; };
 
 // Tensor kinds (tensor id = layer * 32 + kind; globals use layer = 1000).
 enum Kind : uint32_t {
@@ -89,6 +105,7 @@ struct Layer {
   int ln1, wqkv, bqkv, sinks, wo, bo, ln2, wr, br;
   int gu_codes, gu_scales, gu_bias, dn_codes, dn_scales, dn_bias;
   int gu_mx = -1, dn_mx = -1;      // header flags bit 6: the wide block-scaled tensor-core layout (mxfp4_retile_wide)
+  int wqkv_t = -1, wo_t = -1;      // batched mode: the dense weights tiled for the tensor cores (dense_tc_retile)
   int kcache, vcache;
   int cache_len, window;
 };
@@ -109,13 +126,16 @@ struct State {
   int max_decode = 4096;
   int dense_stream = 1, dense_stages = 4, dense_ctas = 296;
   int mega = 0, mega_tab = -1, mega_sync = -1, mega_am_v = -1, mega_am_i = -1, mega_grid = 0, mega_trace = -1, mega_rpart = -1, mega_mx = 0, mega_kc_gu = 8, mega_kc_dn = 8;
+  // batched mode
+  int batched = 0, lm_head_t = -1, a_tiled = -1, xn_all = -1, dig = -1, em = -1, y_part = -1, y_recv = -1, tiles = -1;
+  int ep_rank = 0, ep_world = 1, expert_lo = 0, expert_n = 0, m64_rows16 = 1;
   LoadScope scope;
   int fail_after = -1;
   std::vector<int64_t> next_pos;     // per sequence: the position the next step will run at (-1: prep has not run)
 };
 
 bool synth(B200CudaContext *ctx, Launcher &L, int buf, uint64_t n, uint32_t layer, uint32_t kind, uint32_t seed,
-           int gen, double sigma, int lo = 0, int span = 1) {
+           int gen, double sigma, int lo = 0, int span = 1, uint64_t first = 0) {
   SynthArgs a{};
   a.n = n;
   a.tensor = layer * 32 + kind;
@@ -124,6 +144,7 @@ bool synth(B200CudaContext *ctx, Launcher &L, int buf, uint64_t n, uint32_t laye
   a.c = float(sigma / 209.0232);
   a.lo = lo;
   a.span = span;
+  a.first = first;
   const int blocks = int(std::min<uint64_t>((n + 255) / 256, 148 * 32));
   L("synth_fill", {buf}, a, std::max(1, blocks), 1, 1, 256);
   (void)ctx;

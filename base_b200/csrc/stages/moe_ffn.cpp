@@ -210,7 +210,6 @@ void destroy(uint8_t *mem);
 // load on a loaded instance releases what the earlier load made and loads anew.
 void stage_load(uint8_t *mem) {
   StageIO io(mem);
-  if (io.state<State>()) destroy(mem);
   if (io.data_len < sizeof(MoeLoadHeader)) return stage_fail(mem, 1, "load: payload shorter than header");
   MoeLoadHeader h;
   memcpy(&h, io.data, sizeof(h));
@@ -238,6 +237,7 @@ void stage_load(uint8_t *mem) {
     return stage_fail(mem, 1, "load: the block-scaled path needs hidden and inter to be multiples of 64, at most 2880, and the tiled layout");
   if ((h.flags & 32) && (h.flags & 2))
     return stage_fail(mem, 1, "load: the tensor-core path needs the tiled layout (flags bit 1 must be clear)");
+  if (io.state<State>()) destroy(mem);          // a valid request on a loaded instance: reload
   LoadScope scope;
   if (!scope.begin(mem)) return stage_fail(mem, 2, std::string("load: no CUDA device: ") + cl_b200_last_error());
   B200CudaContext *ctx = io.ctx();

@@ -46,7 +46,7 @@ struct AttnArgs {
   float scale;
   int max_splits;
 };
-struct SynthArgs { unsigned long long n; uint32_t tensor, seed; int kind; float c; int lo, span; };
+struct SynthArgs { unsigned long long n; uint32_t tensor, seed; int kind; float c; int lo, span; unsigned long long first; };
 
 // tensor id = layer * 32 + kind; globals use layer 1000
 enum Kind : uint32_t { kLn1 = 0, kWqkv, kBqkv, kWo, kLn2, kWgu, kWdn, kEmbed = 16, kLnF };
@@ -132,7 +132,6 @@ void destroy(uint8_t *mem);
 // load on a loaded instance releases what the earlier load made and loads anew.
 void stage_load(uint8_t *mem) {
   StageIO io(mem);
-  if (io.state<State>()) destroy(mem);
   if (io.data_len != sizeof(QwenHeader)) return stage_fail(mem, 1, "load: payload must be the 64-byte header");
   QwenHeader h;
   memcpy(&h, io.data, sizeof(h));
@@ -145,6 +144,7 @@ void stage_load(uint8_t *mem) {
   if (h.batch == 0 || h.batch > 4 || h.layers == 0 || h.layers > 128 || h.vocab == 0 || h.max_seq == 0 ||
       h.max_seq > (1u << 20))
     return stage_fail(mem, 1, "load: batch 1..4, layers/vocab/max_seq in range");
+  if (io.state<State>()) destroy(mem);          // a valid request on a loaded instance: reload
   LoadScope scope;
   if (!scope.begin(mem)) return stage_fail(mem, 2, std::string("load: no CUDA device: ") + cl_b200_last_error());
   B200CudaContext *ctx = io.ctx();

@@ -16,6 +16,8 @@ MAGIC = 0x31534F47  # "GOS1"
 PDL, ONE_COLUMN = 1, 4
 PERSISTENT = 32   # the whole decode step as one cooperative persistent kernel (batch 1)
 BLOCK_SCALED = 64 # with PERSISTENT: the experts run on the block-scaled tensor cores (tcgen05.mma kind::mxf4)
+BATCHED = 128     # up to 256 sequences per GPU: dense layers and experts on the tcgen05 tensor cores, every weight read
+                  # once per step for all sequences; with ep_world > 1 expert-parallel over that many GPUs
 
 KIND = dict(ln1=0, wqkv=1, bqkv=2, sinks=3, wo=4, bo=5, ln2=6, wr=7, br=8, gu_codes=9, gu_scales=10, gu_bias=11,
             dn_codes=12, dn_scales=13, dn_bias=14, embed=16, lm_head=17, lnf=18)
@@ -44,12 +46,14 @@ class GptOssConfig:
     flags: int = PDL
     test_skip_fill: int = 0   # failure-path test hook: 1 + the ring fill the persistent kernel's producers leave out
     test_spin: int = 0        # failure-path test hook: iteration limit of the persistent kernel's waits (0: default)
+    ep_rank: int = 0          # BATCHED over several GPUs: this process's rank ...
+    ep_world: int = 0         # ... of this many (0 or 1: one GPU); `batch` is the number of sequences per GPU
 
     def header(self) -> bytes:
-        h = struct.pack("<13I4f4I2I9I", MAGIC, self.layers, self.hidden, self.inter, self.experts, self.top_k,
+        h = struct.pack("<13I4f4I4I7I", MAGIC, self.layers, self.hidden, self.inter, self.experts, self.top_k,
                         self.n_q, self.n_kv, self.head_dim, self.vocab, self.window, self.max_seq, self.batch,
                         self.rope_theta, self.eps, self.alpha, self.limit, self.seed, self.flags, 0, 0,
-                        self.test_skip_fill, self.test_spin, *([0] * 9))
+                        self.test_skip_fill, self.test_spin, self.ep_rank, self.ep_world, *([0] * 7))
         assert len(h) == 128
         return h
 
@@ -113,6 +117,20 @@ class GptOss:
         if timed:
             return toks, struct.unpack("<f", bytes(out[nb:]))[0]
         return toks
+
+    def comm_init(self, comm_id: bytes):
+        """Join the expert-parallel communicator (BATCHED, ep_world > 1): `comm_id` is the 128-byte id rank 0 made
+        with `new_comm_id()` and sent to every rank.  After construction, before the first step."""
+        self.base.execute(self.art.extras["commInit"], comm_id)
+
+    @staticmethod
+    def new_comm_id() -> bytes:
+        import ctypes
+        from . import lib
+        buf = ctypes.create_string_buffer(128)
+        if lib().cl_b200_comm_unique_id(buf) != 0:
+            raise RuntimeError(lib().cl_b200_last_error().decode())
+        return buf.raw
 
     def fill_kv(self):
         """Overwrite every layer's KV cache with the seeded synthetic rows (stage `fillKV`), so that a step at a

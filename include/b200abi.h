@@ -192,6 +192,22 @@ int64_t cl_b200_mem_free(B200CudaContext *ctx);
  * library is non-blocking: work on the legacy default stream (handle 0) is NOT ordered with it. */
 int64_t cl_b200_stream_handle(B200CudaContext *ctx, int32_t stream_id);
 
+/* Collectives for the expert-parallel decode step, over NCCL (libnccl.so.2, loaded on first use).  No
+ * counterpart in the reference, which has no multi-device path (base/src/ffi/cuda.rs:331-336 opens device 0).
+ * One process per GPU: rank 0 makes a 128-byte id (cl_b200_comm_unique_id), every rank gets it by any host
+ * channel and calls cl_b200_comm_init on its context (outside any stream capture).  The two collectives run
+ * on a stream of the context and can be captured into a CUDA graph:
+ *   all_gather: recv[r*bytes .. (r+1)*bytes) on every rank = rank r's send[send_offset .. +bytes);
+ *   all_to_all: rank r receives send[r*bytes .. +bytes) of every rank q into recv[q*bytes .. +bytes).
+ * Every call returns 0 or -1. */
+int32_t cl_b200_comm_unique_id(uint8_t *out128);
+int32_t cl_b200_comm_init(B200CudaContext *ctx, const uint8_t *id128, int32_t rank, int32_t world);
+int32_t cl_b200_comm_world(B200CudaContext *ctx);
+int32_t cl_b200_comm_all_gather(B200CudaContext *ctx, int32_t send_buf, int64_t send_offset, int32_t recv_buf,
+                                int64_t bytes, int32_t stream_id);
+int32_t cl_b200_comm_all_to_all(B200CudaContext *ctx, int32_t send_buf, int32_t recv_buf, int64_t bytes,
+                                int32_t stream_id);
+
 /* Last error text of the calling thread ("" if none); never null. */
 const char *cl_b200_last_error(void);
 

@@ -88,7 +88,7 @@ def test_noalloc_argmax_is_ordered_after_a_kernel_on_the_library_stream():
     ob = L.cl_cuda_create_buffer(c, B * 4)
     for call, seed in enumerate((3, 4)):
         # synth_fill, kind 2: f32 N(0, 1) values from (seed, tensor 77, index), generated on the main stream
-        args = struct.pack("<Q2Iif2i", B * V, 77, seed, 2, 1.0 / 209.0232, 0, 1)
+        args = struct.pack("<Q2Iif2iQ", B * V, 77, seed, 2, 1.0 / 209.0232, 0, 1, 0)
         bind = struct.pack("<i", lb)
         assert L.cl_b200_launch(c, mod, b"synth_fill", 1, bind, args, len(args), 148 * 8, 1, 1, 256, 1, 1, 0, -1, 0) == 0
         rc = L.cl_b200_argmax_noalloc(ctypes.c_void_p(L.cl_b200_buffer_ptr(c, lb)), V, B, V,
