@@ -12,9 +12,13 @@
 //                       dig [K block][position][8 digit rows x 16 B], em [position][96] block exponents
 //   moe_batch_mx_*      units = (expert, pass of <= 16 tokens, segment of <= 16 eight-row groups): N <= 128 rows per
 //                       instruction; producer warp (bulk copies: the segment's codes + scale words and the tokens'
-//                       digits of one chunk per ring slot), scale warp (weights' scale words -> tensor memory), issuer,
-//                       four epilogue warps (each reads the accumulator rows of four tokens, adds the digit rows,
-//                       bias, clamped SwiGLU).
+//                       digits of one chunk per ring slot), four scale warps (weights' scale words -> tensor memory),
+//                       issuer, four epilogue warps (each reads the accumulator rows of four tokens, adds the digit
+//                       rows, bias, clamped SwiGLU).
+// Scale factors in tensor memory: the tensor core's lane quarter q (accumulator rows 32 q ..) takes BOTH operands' scales
+// from its own 32 lanes, so every quarter needs a copy (what tcgen05.cp ... warpx4 does by itself); here the copies are
+// written with tcgen05.st by one warp per quarter.  With one token only quarter 0 carries results, which is why the
+// one-token kernels write a single copy.
 // Routing tables are those of moe_route_tables_many (count / offset / perm).  Every wait is bounded.
 #pragma once
 #include "moe_mx.cuh"
@@ -26,7 +30,7 @@ constexpr int kBmSlots = 5;
 constexpr int kBmBBytes = kBmGroups * (kBmKc * 128 + 64);      // 17408: codes + scale words of a chunk
 constexpr int kBmABytes = kBmKc * kBmTok * 128;                // 16384: digits of a chunk
 constexpr int kBmSlotBytes = kBmBBytes + kBmABytes;
-constexpr int kBmThreads = 224;              // warps 0..3 epilogue, 4 scale words, 5 issuer, 6 producer
+constexpr int kBmThreads = 320;              // warps 0..3 epilogue, 4..7 weights' scale words, 8 issuer, 9 producer
 constexpr int kBmEmStride = 96;
 constexpr int kBmMaxUnits = 192;             // units one CTA can take
 
@@ -156,9 +160,10 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
   const int *count = route + 1, *offset = route + 1 + E, *perm = route + 1 + E + (E + 1) + E;
 
   if (tid == 0) {
-    for (int i = 0; i < kBmSlots; ++i) { mbar_init(&bars->full[i], 1); mbar_init(&bars->empty[i], 1); mbar_init(&bars->sready[i], 1); }
+    for (int i = 0; i < kBmSlots; ++i) { mbar_init(&bars->full[i], 1); mbar_init(&bars->empty[i], 1); }
     mbar_init(&bars->done, 1);
     mbar_init(&bars->uready, 4);
+    for (int i = 0; i < kBmSlots; ++i) mbar_init(&bars->sready[i], 4);
     bars->abort = 0;
   }
   fence_barrier_init();
@@ -198,7 +203,7 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
   __syncthreads();
   const size_t mbytes = mxw_matrix_bytes(kblocks, kBmKc, R);
 
-  if (warp == 6) {
+  if (warp == 9) {
     // ---- producer
     if (lane == 0) {
       uint32_t q = 0;
@@ -219,8 +224,9 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
         }
       }
     }
-  } else if (warp == 4) {
-    // ---- weights' scale words -> tensor memory (this warp shares warp 0's tensor-memory lanes), per ring slot
+  } else if (warp >= 4 && warp < 8) {
+    // ---- weights' scale words -> tensor memory, per ring slot: warp 4 + q writes lane quarter q's copy
+    const uint32_t tq = uint32_t((warp & 3) * 32) << 16;
     uint32_t q = 0;
     for (int ui = 0; ui < n_units; ++ui) {
       const BmUnit u = units[ui];
@@ -237,7 +243,7 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
 #pragma unroll
           for (int i = 0; i < 8; ++i)
             w[i] = (i < 4 && lane + 32 * i < N) ? *reinterpret_cast<const uint32_t *>(sw + size_t(4 * i) * gb + j * 32) : 0u;
-          tc_st_words8(tSFB + s * 16 + j * 8, w);
+          tc_st_words8(tSFB + tq + s * 16 + j * 8, w);
         }
         tc_wait_st();
         tc_fence_before_sync();
@@ -246,7 +252,7 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
       }
       if (!ok) break;
     }
-  } else if (warp == 5) {
+  } else if (warp == 8) {
     // ---- issuer (whole warp, an elected lane issues)
     uint32_t q = 0;
     for (int ui = 0; ui < n_units; ++ui) {
@@ -281,7 +287,8 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
       const BmUnit u = units[ui];
       const int N = u.ng * 8;
       const int off = offset[u.e] + u.pass * kBmTok, nt = min(kBmTok, count[u.e] - u.pass * kBmTok);
-      if (warp == 0) {
+      {
+        // every warp writes its own lane quarter's copy of the tokens' scales.
         // row 32 q + lane of A = digit row (lane & 7) of token 4 q + (lane >> 3); scale byte = exponent - 21 + 3 (7 - digit row)
         const uint32_t adj = 0x01010101u * uint32_t(3 * (7 - (lane & 7)));
         for (int gg = 0; gg < (kblocks + 3) / 4; ++gg) {
@@ -292,7 +299,7 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
             w[qd] = t < nt ? __ldcg(reinterpret_cast<const uint32_t *>(em + size_t(off + t) * kBmEmStride) + gg) + adj - 0x15151515u
                            : 0x7f7f7f7fu;
           }
-          tc_st_cols4(tSFA + 4 * gg, w[0], w[1], w[2], w[3]);
+          tc_st_cols4(tSFA + (uint32_t(warp * 32) << 16) + 4 * gg, w[0], w[1], w[2], w[3]);
         }
         tc_wait_st();
       }

@@ -132,6 +132,14 @@ class GptOss:
             raise RuntimeError(lib().cl_b200_last_error().decode())
         return buf.raw
 
+    STATE = dict(h1=0, xn=1, router_logits=2, topk_idx=3, topk_w=4, act=5, o=6, qkv=7, attn=8, y_part=9)
+
+    def state(self, name: str, count: int, dtype="<f4") -> np.ndarray:
+        """The first `count` elements of an intermediate buffer of the last step (stage `fetchState`)."""
+        out = bytearray(count * np.dtype(dtype).itemsize)
+        self.base.execute_into(self.art.extras["fetchState"], struct.pack("<I", self.STATE[name]), out)
+        return np.frombuffer(bytes(out), dtype=dtype)
+
     def fill_kv(self):
         """Overwrite every layer's KV cache with the seeded synthetic rows (stage `fillKV`), so that a step at a
         late position has a full context without feeding the prompt."""

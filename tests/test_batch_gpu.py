@@ -90,7 +90,7 @@ def test_dense_gemm_accumulator_rows_and_numpy(ctx):
         out, ref = run_gemm(L, c, 64, 128, 5, 0, rows16, 2, np.random.default_rng(1))
         errs[rows16] = rel(out, ref)
     print("max-rel-err by accumulator row placement:", errs)
-    assert errs[1] < 2e-5 and errs[0] > 1e-3
+    assert errs[1] < 2e-5 and errs[0] > 10 * errs[1]
 
 
 @pytest.mark.parametrize("rows,K,B,kind,grid", [(5120, 2880, 32, 0, 148), (2880, 4096, 7, 1, 148), (4096, 2880, 70, 0, 37),

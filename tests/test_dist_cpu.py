@@ -88,3 +88,51 @@ def test_partial_sums_all_reduce_on_every_rank():
         assert p.exitcode == 0
     for _, vals in got:
         assert vals == [[3.0] * 3] * 4
+
+
+def _ep_worker(rank: int, world: int, port: int, out):
+    import numpy as np
+    from base_b200.dist import ep_moe_layer
+    from base_b200.moe import MoeConfig, make_moe_params
+    from oracle import moe_oracle as mo
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    r = Ranks(backend="gloo")
+    cfg = MoeConfig(hidden=64, inter=64, experts=8, top_k=4)
+    p = make_moe_params(cfg, seed=41)
+    p["Wr"] *= 20
+    x_all = np.random.default_rng(42).standard_normal((6, cfg.hidden)).astype(np.float32)     # 3 tokens per rank
+    mine = x_all[rank * 3:(rank + 1) * 3]
+    deq = {}
+
+    def expert(e, row):
+        if e not in deq:
+            deq[e] = (mo.mx_dequant(p["gu_codes"][e], p["gu_scales"][e]), mo.mx_dequant(p["dn_codes"][e], p["dn_scales"][e]))
+        return mo.expert_ffn(row, deq[e][0], p["gu_bias"][e], deq[e][1], p["dn_bias"][e], cfg.alpha, cfg.limit)[0]
+
+    def route(xa):
+        return mo.topk_softmax(mo.router_logits(xa, p["Wr"], p["br"]), cfg.top_k)
+
+    y = ep_moe_layer(r, mine, cfg.experts, cfg.top_k, route, expert)
+    want = mo.moe_ffn(x_all, p)[rank * 3:(rank + 1) * 3]
+    lo, n = expert_range(rank, world, cfg.experts)
+    out.put((rank, float(np.abs(y - want).max() / np.abs(want).max()), sorted(deq), (lo, n), r.broadcast_bytes(b"id-from-0" if rank == 0 else None)))
+    r.barrier()
+    r.close()
+
+
+def test_expert_parallel_exchange_on_two_ranks_equals_the_unsharded_layer():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_ep_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = sorted(out.get(timeout=180) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, err, used, (lo, n), ident in got:
+        assert err < 1e-6                                    # same products, summed per rank then over ranks
+        assert all(lo <= e < lo + n for e in used) and used  # a rank only ever runs its own experts
+        assert ident == b"id-from-0"

@@ -1,0 +1,88 @@
+"""Expert-parallel batched decode on two GPUs (one process per GPU, NCCL all-gather + all-to-all inside the
+step's CUDA graph) against the same batch on one GPU.  Skipped where fewer than two GPUs are visible."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _gpu_count() -> int:
+    import ctypes
+    try:
+        cu = ctypes.CDLL("libcuda.so.1")
+    except OSError:
+        return 0
+    if cu.cuInit(0) != 0:
+        return 0
+    n = ctypes.c_int(0)
+    return n.value if cu.cuDeviceGetCount(ctypes.byref(n)) == 0 else 0
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+CFG = dict(layers=3, hidden=128, inter=192, experts=8, top_k=4, n_q=8, n_kv=2, vocab=512, window=8, max_seq=64, seed=5)
+FIRSTS = [7, 99, 400, 3, 250, 31]
+STEPS = 10
+
+
+def _worker(rank: int, world: int, port: int, out):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    from base_b200.dist import Ranks
+    from base_b200.gptoss import GptOss, GptOssConfig, PDL, BATCHED
+    r = Ranks(backend="gloo")
+    per = len(FIRSTS) // world
+    m = GptOss(GptOssConfig(**CFG, batch=per, flags=PDL | BATCHED, ep_rank=rank, ep_world=world))
+    m.comm_init(r.broadcast_bytes(GptOss.new_comm_id() if rank == 0 else None))
+    toks = FIRSTS[rank * per:(rank + 1) * per]
+    hist, logit_hist = [], []
+    for pos in range(STEPS):
+        r.barrier()
+        got = m.infer(toks, [pos] * per)
+        logit_hist.append(m.logits().copy())
+        hist.append(got.tolist())
+        toks = [int(t) for t in got]
+    out.put((rank, hist, np.stack(logit_hist)))
+    r.barrier()
+    m.close()
+    r.close()
+
+
+@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
+def test_two_gpu_expert_parallel_decode_equals_one_gpu():
+    import torch.multiprocessing as mp
+    from base_b200.gptoss import GptOss, GptOssConfig, PDL, BATCHED
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = sorted(out.get(timeout=600) for _ in procs)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    one = GptOss(GptOssConfig(**CFG, batch=len(FIRSTS), flags=PDL | BATCHED))
+    toks = list(FIRSTS)
+    per = len(FIRSTS) // 2
+    for pos in range(STEPS):
+        nxt = one.infer(toks, [pos] * len(FIRSTS))
+        logits = one.logits()
+        for rank, hist, lg in got:
+            mine = slice(rank * per, (rank + 1) * per)
+            err = float(np.abs(lg[pos] - logits[mine]).max() / np.abs(logits[mine]).max())
+            assert err < 1e-4, f"rank {rank} pos {pos}: {err}"        # only the order of the experts' sum differs
+            for i, b in enumerate(range(rank * per, (rank + 1) * per)):
+                top2 = np.sort(logits[b])[-2:]
+                if top2[1] - top2[0] > 4e-4 * np.abs(logits[b]).max():
+                    assert hist[pos][i] == int(nxt[b])
+        # follow the two-GPU run's tokens so that both sides see the same inputs at every step
+        toks = [t for _, hist, _ in got for t in hist[pos]]
+    one.close()
