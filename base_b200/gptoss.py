@@ -132,7 +132,7 @@ class GptOss:
             raise RuntimeError(lib().cl_b200_last_error().decode())
         return buf.raw
 
-    STATE = dict(h1=0, xn=1, router_logits=2, topk_idx=3, topk_w=4, act=5, o=6, qkv=7, attn=8, y_part=9)
+    STATE = dict(h1=0, xn=1, router_logits=2, topk_idx=3, topk_w=4, act=5, o=6, qkv=7, attn=8, y_part=9, route=10)
 
     def state(self, name: str, count: int, dtype="<f4") -> np.ndarray:
         """The first `count` elements of an intermediate buffer of the last step (stage `fetchState`)."""
@@ -201,6 +201,18 @@ class GptOss:
         out = bytearray(4)
         self.base.execute_into(self.art.extras["benchMoe"], struct.pack("<2I", iters, which), out)
         return struct.unpack("<f", bytes(out))[0]
+
+    BATCH_KERNELS = dict(gate_up=1, down=2, qkv=3, o_proj=4, attention=5)
+
+    def bench_batch(self, which: str, iters: int = 1) -> float:
+        """Milliseconds (device events) for `iters` passes of one kernel of the batched step over every layer."""
+        out = bytearray(4)
+        self.base.execute_into(self.art.extras["benchBatch"], struct.pack("<2I", self.BATCH_KERNELS[which], iters), out)
+        return struct.unpack("<f", bytes(out))[0]
+
+    def expert_counts(self) -> np.ndarray:
+        """Tokens per expert in the last layer of the last step (all experts, from the routing tables)."""
+        return self.state("route", 1 + self.cfg.experts, "<i4")[1:]
 
     def close(self):
         self.base.close()

@@ -386,6 +386,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--prompt", type=int, default=PROMPT)
+    ap.add_argument("--batch", type=int, default=32,
+                    help="sequences decoded together, over all GPUs (default 32: BASELINE config 3 at batch 32, sharded over "
+                         "the GPUs: strong scaling).  1 = the batch-1 persistent step kernel, a full replica per GPU")
+    ap.add_argument("--no-batch1", action="store_true",
+                    help="with --batch > 1 on one GPU: do not also measure the batch-1 persistent kernel")
     ap.add_argument("--repeats", type=int, default=5,
                     help="how many times the K-step timed loop runs; the line reports the median repeat and the spread")
     ap.add_argument("--workload", choices=("gptoss", "qwen2", "prefill"), default="gptoss",
@@ -405,6 +410,14 @@ def main():
         return run_qwen2(a, rank)
     if a.workload == "prefill":
         return run_prefill(a, rank)
+    if a.batch > 1:
+        return run_batched(a, rank, world, local)
+    return run_batch1(a, rank, world, local)
+
+
+def run_batch1(a, rank: int, world: int, local: int, ranks=None, emit: bool = True):
+    """BASELINE config 3 at batch 1 per GPU: the persistent step kernel (or the per-operation graph); under
+    torchrun every rank decodes its own sequence on a full replica (weak scaling, no data-path collective)."""
     from base_b200.gptoss import GPT_OSS_20B, GptOss, PDL, PERSISTENT, BLOCK_SCALED
     import dataclasses
     mx = a.step == "persistent" and a.experts == "block-scaled"
@@ -436,7 +449,9 @@ def main():
         return
 
     from base_b200.dist import Ranks
-    ranks = Ranks("nccl" if world > 1 else None)
+    own_ranks = ranks is None
+    if own_ranks:
+        ranks = Ranks("nccl" if world > 1 else None)
     barrier, max_over_ranks = ranks.barrier, ranks.max
 
     rng0 = np.random.default_rng(1000 * 3 + rank)
@@ -547,8 +562,135 @@ def main():
                         "reported": "median", "min_tokens_per_s": world * a.steps / (max(rep_ms) * 1e-3),
                         "max_tokens_per_s": world * a.steps / (min(rep_ms) * 1e-3)}}
     m.close()
-    if rank == 0:
+    if rank == 0 and emit:
         line["cpu_baseline"] = cpu_baseline(cfg, a.prompt)
+        print(json.dumps(line))
+    if own_ranks:
+        ranks.close()
+    return line
+
+
+
+def run_batched(a, rank: int, world: int, local: int):
+    """BASELINE config 3 at batch `--batch` (default 32): ONE model over all GPUs.  Every GPU holds batch / N of the
+    sequences (their KV caches; attention and dense weights replicated) and experts / N of every layer's experts;
+    per layer an all-gather of the normalised hidden states and an all-to-all of the experts' partial sums (NCCL,
+    captured in the step's CUDA graph).  The work is fixed as N grows: strong scaling.  On one GPU the same
+    launches run without the collectives."""
+    import dataclasses
+    from base_b200.gptoss import GPT_OSS_20B, GptOss, PDL, BATCHED
+    from base_b200.dist import Ranks
+    Bg = a.batch
+    if Bg % world or GPT_OSS_20B.experts % world:
+        raise SystemExit(f"--batch {Bg} and the {GPT_OSS_20B.experts} experts must be divisible by the {world} GPUs")
+    per = Bg // world
+    reps = max(1, a.repeats)
+    cfg = dataclasses.replace(GPT_OSS_20B, batch=per, max_seq=a.prompt + a.warmup + (reps + 1) * a.steps + 8,
+                              flags=PDL | BATCHED, ep_rank=rank, ep_world=world)
+    config = {"workload": f"gpt-oss-20b decode, {Bg} sequences, 2048-token prompts, greedy (BASELINE config 3, batch {Bg})",
+              "layers": cfg.layers, "hidden": cfg.hidden, "experts": cfg.experts, "top_k": cfg.top_k, "vocab": cfg.vocab,
+              "context": a.prompt, "global_batch": Bg, "batch_per_gpu": per,
+              "parallelism": (f"expert parallel x{world} (experts {cfg.experts // world} per GPU, NCCL all-gather + all-to-all per "
+                              f"layer), sequences and attention data parallel x{world}") if world > 1 else "single GPU",
+              "step": "one CUDA graph per step: tcgen05 skinny GEMMs (dense), block-scaled tcgen05 expert kernel, split-KV attention",
+              "l2": "each step streams >= 3.7 GB of weights per GPU, far larger than L2; no flush needed"}
+    if a.impl == "reference":
+        if rank != 0:
+            return
+        one = dataclasses.replace(GPT_OSS_20B, max_seq=a.prompt + a.steps + a.warmup + 8)
+        base, t_step, n_timed = cpu_reference(one, a.prompt, a.steps, a.warmup)
+        base["sample"] += (f"; the reference decodes one sequence per call (no batching), so {Bg} sequences cost {Bg} such "
+                           "steps and its tokens/s does not depend on the batch")
+        config = dict(config, step="C port of the reference's CPU path, one sequence and one decode step per call",
+                      parallelism=f"{base['cores']} host threads")
+        line = {"metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps,
+                "steps_timed": n_timed, "warmup": a.warmup, "ms_per_step": t_step * 1e3 * Bg, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "mxfp4 weights, f32 accumulate", "data": "synthetic",
+                "config": config, "impl": "reference", "cpu_baseline": base,
+                "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    ranks = Ranks("nccl" if world > 1 else None)
+    barrier, max_over_ranks = ranks.barrier, ranks.max
+    m = GptOss(cfg)
+    if world > 1:
+        m.comm_init(ranks.broadcast_bytes(GptOss.new_comm_id() if rank == 0 else None))
+    rng = np.random.default_rng(1000 * 3 + 17)
+    prompt = rng.integers(0, cfg.vocab, size=(a.prompt, Bg))[:, rank * per:(rank + 1) * per]
+    toks = None
+    for pos in range(a.prompt):
+        toks = m.infer(prompt[pos].tolist(), [pos] * per)
+    toks, pos = [int(t) for t in toks], a.prompt
+    m.prep(toks, [pos] * per)
+    if a.warmup:
+        w = m.decode(a.warmup)
+        toks, pos = [int(t) for t in w[-1]], pos + a.warmup
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    sampler.mark()
+    rep_ms = []
+    for _ in range(reps):
+        barrier()
+        m.prep(toks, [pos] * per)
+        out, ms_r = m.decode(a.steps, timed=True)
+        barrier()
+        rep_ms.append(max_over_ranks(ms_r))
+        toks, pos = [int(t) for t in out[-1]], pos + a.steps
+    order = sorted(range(len(rep_ms)), key=lambda i: rep_ms[i])
+    mid = order[len(order) // 2]
+    ms = rep_ms[mid]
+    pos_mid = pos - (len(rep_ms) - mid) * a.steps
+    value = Bg * a.steps / (ms * 1e-3)
+
+    # end to end: one execute_into per step with host buffers (tokens and positions in, next tokens out)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(a.steps):
+        toks = [int(t) for t in m.infer(toks, [pos + i] * per)]
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    barrier()
+    clocks = sampler.stop()
+
+    # roofline of the dominant kernel, timed alone over every layer's weights with the last step's routing
+    peak, peak_kind = measured_peak_gbs()
+    lo, n_e = rank * (cfg.experts // world), cfg.experts // world
+    hit = int((m.expert_counts()[lo:lo + n_e] > 0).sum())
+    iters = 3
+    gu_ms = min(m.bench_batch("gate_up", iters) for _ in range(3))
+    dn_ms = min(m.bench_batch("down", iters) for _ in range(3))
+    qkv_ms = min(m.bench_batch("qkv", iters) for _ in range(3))
+    at_ms = min(m.bench_batch("attention", iters) for _ in range(3))
+    per_launch = lambda t: t * 1e-3 / (iters * cfg.layers)
+    gu_bytes, dn_bytes = cfg.gate_up_bytes(hit), cfg.down_bytes(hit)
+    qkv_bytes = (cfg.n_q + 2 * cfg.n_kv) * cfg.head_dim * cfg.hidden * 2
+    step_bytes = cfg.step_bytes(pos_mid + a.steps // 2, experts_hit=hit)
+    step_s = ms * 1e-3 / a.steps
+    achieved = gu_bytes / per_launch(gu_ms) / 1e9
+    roof = {"kernel": "moe_batch_mx_gate_up", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "frac": achieved / peak, "peak_source": peak_kind, "traffic": None,
+            "bytes_per_launch": gu_bytes, "us_per_launch": per_launch(gu_ms) * 1e6, "experts_hit_per_gpu": hit,
+            "other_kernels": {"moe_batch_mx_down": {"gbs": dn_bytes / per_launch(dn_ms) / 1e9, "us_per_launch": per_launch(dn_ms) * 1e6},
+                              "dense_tc_gemm_qkv": {"gbs": qkv_bytes / per_launch(qkv_ms) / 1e9, "us_per_launch": per_launch(qkv_ms) * 1e6},
+                              "attn_decode": {"us_per_launch": per_launch(at_ms) * 1e6}},
+            "whole_step": {"bytes_per_gpu": step_bytes, "achieved": step_bytes / step_s / 1e9, "frac": step_bytes / step_s / 1e9 / peak}}
+    launches_per_step = 1 + cfg.layers * 14 + 3
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup,
+            "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "mxfp4 experts / bf16 dense weights, f32 accumulate", "data": "synthetic", "config": config,
+            "e2e": {"value": Bg * a.steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 8 * per, "d2h_bytes_per_step": 4 * per},
+            "gpu_launches": a.steps * len(rep_ms) * launches_per_step, "clocks": clocks, "roofline": roof,
+            "repeats": {"n": len(rep_ms), "ms_per_step": [round(r / a.steps, 5) for r in rep_ms], "reported": "median",
+                        "min_tokens_per_s": Bg * a.steps / (max(rep_ms) * 1e-3), "max_tokens_per_s": Bg * a.steps / (min(rep_ms) * 1e-3)}}
+    m.close()
+    if world == 1 and not a.no_batch1:
+        # the batch-1 workload of the same config on the same GPU: the persistent step kernel
+        b1 = run_batch1(a, rank, world, local, ranks=ranks, emit=False)
+        line["batch1"] = {k: b1[k] for k in ("value", "ms_per_step", "e2e", "roofline", "repeats", "gpu_launches")}
+        line["batch1"]["config"] = b1["config"]
+    if rank == 0:
+        line["cpu_baseline"] = cpu_baseline(dataclasses.replace(GPT_OSS_20B), a.prompt)
         print(json.dumps(line))
     ranks.close()
 
