@@ -107,7 +107,7 @@ struct BatchMxArgs {
 struct BmUnit { int16_t e, pass, g0, ng; };
 
 struct BmBars {
-  uint64_t full[kBmSlots], empty[kBmSlots], sready[kBmSlots], done, uready;
+  uint64_t full[kBmSlots], empty[kBmSlots], sready[kBmSlots], done[2], uready[2];
   uint32_t tmem_base;
   int abort, n_units, u_base;
 };
@@ -161,8 +161,7 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
 
   if (tid == 0) {
     for (int i = 0; i < kBmSlots; ++i) { mbar_init(&bars->full[i], 1); mbar_init(&bars->empty[i], 1); }
-    mbar_init(&bars->done, 1);
-    mbar_init(&bars->uready, 4);
+    for (int i = 0; i < 2; ++i) { mbar_init(&bars->done[i], 1); mbar_init(&bars->uready[i], 4); }
     for (int i = 0; i < kBmSlots; ++i) mbar_init(&bars->sready[i], 4);
     bars->abort = 0;
   }
@@ -172,7 +171,8 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = bars->tmem_base;
-  const uint32_t tSFA = tmem, tSFB = tmem + 96, tD = tmem + 192;
+  // columns: the tokens' scales of two units in flight [0, 192), the weights' scales per ring slot [192, 232), two accumulators [256, 512)
+  const uint32_t tSFA = tmem, tSFB = tmem + 192, tD = tmem + 256;
   pdl_wait();
   pdl_launch_dependents();
 
@@ -239,11 +239,11 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
         const int kcc = min(kBmKc, kblocks - c * kBmKc), gb = mxw_group_bytes(kcc);
         const uint8_t *sw = ring + size_t(s) * kBmSlotBytes + size_t(lane >> 3) * gb + kcc * 128 + (lane & 7) * 4;
         for (int j = 0; j < (kcc + 3) / 4; ++j) {
-          uint32_t w[8];
+          uint32_t w[4];
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            w[i] = (i < 4 && lane + 32 * i < N) ? *reinterpret_cast<const uint32_t *>(sw + size_t(4 * i) * gb + j * 32) : 0u;
-          tc_st_words8(tSFB + tq + s * 16 + j * 8, w);
+          for (int i = 0; i < 4; ++i)
+            w[i] = lane + 32 * i < N ? *reinterpret_cast<const uint32_t *>(sw + size_t(4 * i) * gb + j * 32) : 0u;
+          tc_st_cols4(tSFB + tq + s * 8 + j * 4, w[0], w[1], w[2], w[3]);
         }
         tc_wait_st();
         tc_fence_before_sync();
@@ -258,7 +258,8 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
     for (int ui = 0; ui < n_units; ++ui) {
       const BmUnit u = units[ui];
       const int N = u.ng * 8;
-      if (!bm_wait(&bars->uready, ui & 1, bars, status, 74)) break;      // the tokens' scales are in place, the accumulator is free
+      if (!bm_wait(&bars->uready[ui & 1], (ui >> 1) & 1, bars, status, 74)) break;      // this unit's token scales are in place, its accumulator is free
+      const uint32_t tDu = tD + uint32_t(ui & 1) * 128u, tSFAu = tSFA + uint32_t(ui & 1) * 96u;
       tc_fence_after_sync();
       const uint32_t id0 = mx_idesc(128, N, 0, 0), id2 = mx_idesc(128, N, 2, 2);
       bool ok = true;
@@ -272,41 +273,48 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
         for (int pp = 0; 4 * pp < kcc; ++pp) {
           const uint64_t da = tc_smem_desc(sa + uint32_t(4 * pp) * (kBmTok * 128), kBmTok * 128, 128);
           const uint64_t db = tc_smem_desc(sb + uint32_t(4 * pp) * 128, 128, uint32_t(gb));
-          bm_mma_pair_warp(tD, da, db, id0, id2, tSFA + 4 * uint32_t(c * (kBmKc >> 2) + pp), tSFB + s * 16 + uint32_t(pp) * 8,
+          bm_mma_pair_warp(tDu, da, db, id0, id2, tSFAu + 4 * uint32_t(c * (kBmKc >> 2) + pp), tSFB + s * 8 + uint32_t(pp) * 4,
                            !(c == 0 && pp == 0), 4 * pp + 2 < kcc, uint32_t(2 * kBmTok * 128) >> 4, 256u >> 4);
         }
         tc_commit_warp(&bars->empty[s], true);
-        tc_commit_warp(&bars->done, c == nch - 1);
+        tc_commit_warp(&bars->done[ui & 1], c == nch - 1);
         __syncwarp();
       }
       if (!ok) break;
     }
   } else if (warp < 4) {
-    // ---- tokens' scales (warp 0) and the epilogue
+    // ---- the tokens' scales (every warp writes its own lane quarter's copy, one unit ahead of the issuer) and the epilogue
+    auto stage_scales = [&](int ui) {
+      const BmUnit u = units[ui];
+      const int off = offset[u.e] + u.pass * kBmTok, nt = min(kBmTok, count[u.e] - u.pass * kBmTok);
+      // row 32 q + lane of A = digit row (lane & 7) of token 4 q + (lane >> 3); scale byte = exponent - 21 + 3 (7 - digit row)
+      const uint32_t adj = 0x01010101u * uint32_t(3 * (7 - (lane & 7)));
+      const uint32_t base = tSFA + uint32_t(ui & 1) * 96u + (uint32_t(warp * 32) << 16);
+      for (int gg = 0; gg < (kblocks + 3) / 4; ++gg) {
+        uint32_t w[4];
+#pragma unroll
+        for (int qd = 0; qd < 4; ++qd) {
+          const int t = 4 * qd + (lane >> 3);
+          w[qd] = t < nt ? __ldcg(reinterpret_cast<const uint32_t *>(em + size_t(off + t) * kBmEmStride) + gg) + adj - 0x15151515u
+                         : 0x7f7f7f7fu;
+        }
+        tc_st_cols4(base + 4 * gg, w[0], w[1], w[2], w[3]);
+      }
+      tc_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->uready[ui & 1]);
+    };
+    if (n_units > 0) stage_scales(0);
     for (int ui = 0; ui < n_units; ++ui) {
       const BmUnit u = units[ui];
       const int N = u.ng * 8;
       const int off = offset[u.e] + u.pass * kBmTok, nt = min(kBmTok, count[u.e] - u.pass * kBmTok);
-      {
-        // every warp writes its own lane quarter's copy of the tokens' scales.
-        // row 32 q + lane of A = digit row (lane & 7) of token 4 q + (lane >> 3); scale byte = exponent - 21 + 3 (7 - digit row)
-        const uint32_t adj = 0x01010101u * uint32_t(3 * (7 - (lane & 7)));
-        for (int gg = 0; gg < (kblocks + 3) / 4; ++gg) {
-          uint32_t w[4];
-#pragma unroll
-          for (int qd = 0; qd < 4; ++qd) {
-            const int t = 4 * qd + (lane >> 3);
-            w[qd] = t < nt ? __ldcg(reinterpret_cast<const uint32_t *>(em + size_t(off + t) * kBmEmStride) + gg) + adj - 0x15151515u
-                           : 0x7f7f7f7fu;
-          }
-          tc_st_cols4(tSFA + (uint32_t(warp * 32) << 16) + 4 * gg, w[0], w[1], w[2], w[3]);
-        }
-        tc_wait_st();
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->uready);
-      if (!bm_wait(&bars->done, ui & 1, bars, status, 76)) break;
+      // the next unit's scales go into the other buffer (its instructions, two units back, are complete: their
+      // accumulator was read in the last iteration), so the issuer never waits for this warp
+      if (ui + 1 < n_units) stage_scales(ui + 1);
+      const uint32_t tDu = tD + uint32_t(ui & 1) * 128u;
+      if (!bm_wait(&bars->done[ui & 1], (ui >> 1) & 1, bars, status, 76)) break;
       tc_fence_after_sync();
       const int tt = 4 * warp + (lane >> 3);
       const int asg = tt < nt ? perm[off + tt] : 0;
@@ -314,8 +322,8 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
         float v[32];
         {
           float lo16[16], hi16[16];
-          tc_ld16(tD + (uint32_t(warp * 32) << 16) + uint32_t(c0), lo16);
-          tc_ld16(tD + (uint32_t(warp * 32) << 16) + uint32_t(c0 + 16), hi16);
+          tc_ld16(tDu + (uint32_t(warp * 32) << 16) + uint32_t(c0), lo16);
+          tc_ld16(tDu + (uint32_t(warp * 32) << 16) + uint32_t(c0 + 16), hi16);
 #pragma unroll
           for (int i = 0; i < 16; ++i) { v[i] = lo16[i]; v[16 + i] = hi16[i]; }
         }

@@ -143,6 +143,7 @@ B200_DEVICE void cons_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kMegaConsThr
 
 // Bounded mbarrier wait that gives up quickly once the CTA is aborted.
 B200_DEVICE bool mega_wait(uint64_t *bar, uint32_t parity, MegaSmem *sm, int *status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;       // the common case: the data is already there
   const uint32_t lim = *reinterpret_cast<volatile int *>(&sm->abort) ? 4096u : sm->spin;
   for (uint32_t i = 0; i < lim; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
