@@ -21,8 +21,8 @@
 constexpr int kBdTokens = 32;          // tokens per pass
 constexpr int kBdRows = 64;            // A rows per pass (hi + lo)
 constexpr int kBdMaxGroups = 16;       // row groups per unit: N <= 128
-constexpr int kBdSlots = 6;
-constexpr int kBdSlotBytes = 8192 + kBdMaxGroups * 1024;      // A piece + B piece of one K chunk
+constexpr int kBdSlots = 16;          // at most; the ring holds as many slots as fit (a slot = the A piece + this CTA's B piece of one K chunk)
+constexpr int kBdRingBytes = 6 * (8192 + kBdMaxGroups * 1024);
 constexpr int kBdThreads = 192;        // warps 0..3: epilogue, warp 4: producer, warp 5: issuer
 constexpr uint32_t kBdSpin = 1u << 22;
 
@@ -145,18 +145,21 @@ B200_DEVICE bool bd_wait(uint64_t *bar, uint32_t parity, BdBars *b, int *status,
 }
 
 constexpr int kBdStageStride = kBdMaxGroups * 8 + 1;      // floats per staged accumulator row (padded)
-B200_DEVICE int bd_smem_bytes() { return kBdSlots * kBdSlotBytes + kBdRows * kBdStageStride * 4 + int(sizeof(BdBars)) + 64; }
+B200_DEVICE int bd_smem_bytes() { return kBdRingBytes + kBdRows * kBdStageStride * 4 + int(sizeof(BdBars)) + 64; }
 
 extern "C" __global__ void __launch_bounds__(kBdThreads, 1)
 dense_tc_gemm(const uint8_t *__restrict__ Wt, const uint8_t *__restrict__ At, const float *__restrict__ bias,
               const float *__restrict__ res, float *__restrict__ out, int *__restrict__ status, DenseTcArgs a) {
   uint8_t *ring = dyn_smem;
-  float *stage = reinterpret_cast<float *>(dyn_smem + kBdSlots * kBdSlotBytes);
-  BdBars *bars = reinterpret_cast<BdBars *>(dyn_smem + kBdSlots * kBdSlotBytes + kBdRows * kBdStageStride * 4);
+  float *stage = reinterpret_cast<float *>(dyn_smem + kBdRingBytes);
+  BdBars *bars = reinterpret_cast<BdBars *>(dyn_smem + kBdRingBytes + kBdRows * kBdStageStride * 4);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int RG = a.rows >> 3, nchunks = a.K >> 6, passes = (a.B + kBdTokens - 1) / kBdTokens;
   const int g_lo = int((long long)RG * blockIdx.x / gridDim.x), g_hi = int((long long)RG * (blockIdx.x + 1) / gridDim.x);
   const int units = (g_hi - g_lo + kBdMaxGroups - 1) / kBdMaxGroups, jobs = units * passes;
+  // few rows per CTA (qkv, o-proj): small slots, many of them in flight; many rows (lm_head): 6 slots of 24 KB
+  const uint32_t slot_bytes = 8192u + uint32_t(max(1, min(kBdMaxGroups, g_hi - g_lo))) * 1024u;
+  const uint32_t n_slots = min(uint32_t(kBdSlots), uint32_t(kBdRingBytes) / slot_bytes);
 
   if (tid == 0) {
     for (int i = 0; i < kBdSlots; ++i) { mbar_init(&bars->full[i], 1); mbar_init(&bars->empty[i], 1); }
@@ -180,9 +183,9 @@ dense_tc_gemm(const uint8_t *__restrict__ Wt, const uint8_t *__restrict__ At, co
         const int u = j / passes, pass = j % passes;
         const int g0 = g_lo + u * kBdMaxGroups, ng = min(kBdMaxGroups, g_hi - g0);
         for (int c = 0; c < nchunks; ++c, ++q) {
-          const uint32_t s = q % kBdSlots;
-          if (q >= kBdSlots && !bd_wait(&bars->empty[s], ((q / kBdSlots) - 1) & 1, bars, status, 61)) { j = jobs; break; }
-          uint8_t *dst = ring + size_t(s) * kBdSlotBytes;
+          const uint32_t s = q % n_slots;
+          if (q >= n_slots && !bd_wait(&bars->empty[s], ((q / n_slots) - 1) & 1, bars, status, 61)) { j = jobs; break; }
+          uint8_t *dst = ring + size_t(s) * slot_bytes;
           mbar_expect_tx(&bars->full[s], 8192u + uint32_t(ng) * 1024u);
           bulk_g2s(dst, At + (size_t(pass) * nchunks + c) * 8192, 8192u, &bars->full[s]);
           bulk_g2s(dst + 8192, Wt + (size_t(c) * RG + g0) * 1024, uint32_t(ng) * 1024u, &bars->full[s]);
@@ -202,11 +205,11 @@ dense_tc_gemm(const uint8_t *__restrict__ Wt, const uint8_t *__restrict__ At, co
         const uint32_t idesc = tc_idesc_bf16(kBdRows, N);
         bool ok = true;
         for (int c = 0; c < nchunks; ++c, ++q) {
-          const uint32_t s = q % kBdSlots;
-          ok = bd_wait(&bars->full[s], (q / kBdSlots) & 1, bars, status, 63);
+          const uint32_t s = q % n_slots;
+          ok = bd_wait(&bars->full[s], (q / n_slots) & 1, bars, status, 63);
           if (!ok) break;
           tc_fence_after_sync();
-          const uint32_t sa = smem_u32(ring + size_t(s) * kBdSlotBytes), sb = sa + 8192;
+          const uint32_t sa = smem_u32(ring + size_t(s) * slot_bytes), sb = sa + 8192;
 #pragma unroll
           for (int st = 0; st < 4; ++st) {
             const uint64_t da = tc_smem_desc(sa + st * 2 * (kBdRows * 16), kBdRows * 16, 128);

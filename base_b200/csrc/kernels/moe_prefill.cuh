@@ -272,6 +272,8 @@ struct RouterManyArgs { int T, H, E; };
 extern "C" __global__ void __launch_bounds__(256)
 moe_router_many(const float *__restrict__ Wr, const float *__restrict__ br, const float *__restrict__ x,
                 float *__restrict__ logits, RouterManyArgs a) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int t0 = blockIdx.x * 4, nt = min(4, a.T - t0), n4 = a.H >> 2;
   float4 *xs = reinterpret_cast<float4 *>(dyn_smem);            // [4][H]
@@ -309,6 +311,8 @@ struct TablesManyArgs { int A, E, lo, n; };   // token tiles only for experts [l
 extern "C" __global__ void __launch_bounds__(1024)
 moe_route_tables_many(const int *__restrict__ topk_idx, int *__restrict__ route, int *__restrict__ tiles,
                       TablesManyArgs a) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int A = a.A, E = a.E, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int *n_active = route, *count = route + 1, *offset = route + 1 + E, *active = offset + E + 1, *perm = active + E;
   __shared__ int s_count[128], s_offset[129], s_run[128];
@@ -386,6 +390,8 @@ struct CombineRangeArgs { int H, top_k, lo, n; };
 extern "C" __global__ void __launch_bounds__(256)
 moe_combine_range(const float *__restrict__ o, const float *__restrict__ topk_w, const int *__restrict__ topk_idx,
                   float *__restrict__ y, CombineRangeArgs a) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.y;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= a.H) return;

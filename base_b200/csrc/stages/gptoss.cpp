@@ -83,6 +83,8 @@ constexpr int kMegaThreads = 512;
 constexpr int kMegaSmemBytes = 7 * 25088 + 56832;   // ring + MegaSmem (mega_decode.cuh): all 227 KB
 constexpr int kMxSlotBytes = 25088;
 struct RetileWideArgs { int R, K, n_mat, kc; };
+struct AttnBatchArgs { int NQ, NKV, B, cache_len, window, max_pos, qkv_stride; float scale; int max_splits, S; };
+constexpr int kAbThreads = 256, kAbSmemBytes = 2 * 2 * 128 * 72 * 2 + 8 * 64 * 4 + 8 * 128 * 4 + 32;
 struct DenseRetileArgs { int rows, K; };
 struct RowsToAArgs { int K, B, mode, n_parts; long long part_stride; float eps; };
 struct DenseTcArgs { int rows, K, B, kind, m64_rows16, out_stride; };
@@ -91,7 +93,7 @@ struct BatchMxArgs { MoeDims d; int lo, n, P; };
 struct RouterManyArgs { int T, H, E; };
 struct TablesManyArgs { int A, E, lo, n; };
 struct CombineRangeArgs { int H, top_k, lo, n; };
-constexpr int kBdThreads = 192, kBdSmemBytes = 6 * (8192 + 16 * 1024) + 64 * 129 * 4 + 256;
+constexpr int kBdThreads = 192, kBdSmemBytes = 6 * (8192 + 16 * 1024) + 64 * 129 * 4 + 512;
 constexpr int kBmThreads = 320, kBmSmemBytes = 5 * (16 * (8 * 128 + 64) + 8 * 16 * 128) + 192 * 8 + 256;
 struct SynthArgs { unsigned long long n; uint32_t tensor, seed; int kind; float c; int lo, span; unsigned long long first; };
 

@@ -202,7 +202,7 @@ class GptOss:
         self.base.execute_into(self.art.extras["benchMoe"], struct.pack("<2I", iters, which), out)
         return struct.unpack("<f", bytes(out))[0]
 
-    BATCH_KERNELS = dict(gate_up=1, down=2, qkv=3, o_proj=4, attention=5)
+    BATCH_KERNELS = dict(gate_up=1, down=2, qkv=3, o_proj=4, attention=5, lm_head=6)
 
     def bench_batch(self, which: str, iters: int = 1) -> float:
         """Milliseconds (device events) for `iters` passes of one kernel of the batched step over every layer."""

@@ -662,6 +662,8 @@ def run_batched(a, rank: int, world: int, local: int):
     dn_ms = min(m.bench_batch("down", iters) for _ in range(3))
     qkv_ms = min(m.bench_batch("qkv", iters) for _ in range(3))
     at_ms = min(m.bench_batch("attention", iters) for _ in range(3))
+    op_ms = min(m.bench_batch("o_proj", iters) for _ in range(3))
+    lm_ms = min(m.bench_batch("lm_head", iters) for _ in range(3))
     per_launch = lambda t: t * 1e-3 / (iters * cfg.layers)
     gu_bytes, dn_bytes = cfg.gate_up_bytes(hit), cfg.down_bytes(hit)
     qkv_bytes = (cfg.n_q + 2 * cfg.n_kv) * cfg.head_dim * cfg.hidden * 2
@@ -673,7 +675,9 @@ def run_batched(a, rank: int, world: int, local: int):
             "bytes_per_launch": gu_bytes, "us_per_launch": per_launch(gu_ms) * 1e6, "experts_hit_per_gpu": hit,
             "other_kernels": {"moe_batch_mx_down": {"gbs": dn_bytes / per_launch(dn_ms) / 1e9, "us_per_launch": per_launch(dn_ms) * 1e6},
                               "dense_tc_gemm_qkv": {"gbs": qkv_bytes / per_launch(qkv_ms) / 1e9, "us_per_launch": per_launch(qkv_ms) * 1e6},
-                              "attn_decode": {"us_per_launch": per_launch(at_ms) * 1e6}},
+                              "dense_tc_gemm_o_proj": {"gbs": cfg.hidden * cfg.n_q * cfg.head_dim * 2 / per_launch(op_ms) / 1e9, "us_per_launch": per_launch(op_ms) * 1e6},
+                              "dense_tc_gemm_lm_head": {"gbs": cfg.vocab * cfg.hidden * 2 / (lm_ms * 1e-3 / iters) / 1e9, "us_per_launch": lm_ms * 1e3 / iters},
+                              "attn_decode_batch": {"us_per_launch": per_launch(at_ms) * 1e6}},
             "whole_step": {"bytes_per_gpu": step_bytes, "achieved": step_bytes / step_s / 1e9, "frac": step_bytes / step_s / 1e9 / peak}}
     launches_per_step = 1 + cfg.layers * 14 + 3
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup,
