@@ -144,6 +144,23 @@ B200_DEVICE bool bd_wait(uint64_t *bar, uint32_t parity, BdBars *b, int *status,
   return false;
 }
 
+// Four K = 16 instructions over one K chunk of 64 (the operands advance by two column groups each: 2 x 64 rows x 16 B
+// of A, 2 x 128 B of B), issued by an elected lane of the converged warp.
+B200_DEVICE void bd_mma4_warp(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool accumulate_first) {
+  asm volatile(
+      "{\n.reg .pred p, q, e;\n.reg .b64 a1, a2, a3, b1, b2, b3;\n"
+      "elect.sync _|e, 0xffffffff;\n"
+      "setp.ne.b32 p, %4, 0;\nsetp.eq.b32 q, %4, %4;\n"
+      "add.u64 a1, %1, 128;\nadd.u64 a2, %1, 256;\nadd.u64 a3, %1, 384;\n"
+      "add.u64 b1, %2, 16;\nadd.u64 b2, %2, 32;\nadd.u64 b3, %2, 48;\n"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, q;\n"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], a2, b2, %3, q;\n"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], a3, b3, %3, q;\n}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(uint32_t(accumulate_first))
+      : "memory");
+}
+
 constexpr int kBdStageStride = kBdMaxGroups * 8 + 1;      // floats per staged accumulator row (padded)
 B200_DEVICE int bd_smem_bytes() { return kBdRingBytes + kBdRows * kBdStageStride * 4 + int(sizeof(BdBars)) + 64; }
 
@@ -193,34 +210,29 @@ dense_tc_gemm(const uint8_t *__restrict__ Wt, const uint8_t *__restrict__ At, co
       }
     }
   } else if (warp == 5) {
-    // ---- issuer
-    if (lane == 0) {
-      uint32_t q = 0;
-      for (int j = 0; j < jobs; ++j) {
-        const int u = j / passes;
-        const int g0 = g_lo + u * kBdMaxGroups, ng = min(kBdMaxGroups, g_hi - g0), N = ng * 8;
-        const uint32_t acc = tmem + uint32_t(j & 1) * 128u;
-        if (j >= 2 && !bd_wait(&bars->dfree[j & 1], ((j >> 1) - 1) & 1, bars, status, 62)) break;
-        tc_fence_after_sync();
-        const uint32_t idesc = tc_idesc_bf16(kBdRows, N);
-        bool ok = true;
-        for (int c = 0; c < nchunks; ++c, ++q) {
-          const uint32_t s = q % n_slots;
-          ok = bd_wait(&bars->full[s], (q / n_slots) & 1, bars, status, 63);
-          if (!ok) break;
-          tc_fence_after_sync();
-          const uint32_t sa = smem_u32(ring + size_t(s) * slot_bytes), sb = sa + 8192;
-#pragma unroll
-          for (int st = 0; st < 4; ++st) {
-            const uint64_t da = tc_smem_desc(sa + st * 2 * (kBdRows * 16), kBdRows * 16, 128);
-            const uint64_t db = tc_smem_desc(sb + st * 2 * 128, 128, 1024);
-            tc_mma_bf16(acc, da, db, idesc, c > 0 || st > 0);
-          }
-          tc_commit(&bars->empty[s]);
-        }
+    // ---- issuer: the whole warp runs the loop, an elected lane issues (operands stay in uniform registers)
+    uint32_t q = 0;
+    for (int j = 0; j < jobs; ++j) {
+      const int u = j / passes;
+      const int g0 = g_lo + u * kBdMaxGroups, ng = min(kBdMaxGroups, g_hi - g0), N = ng * 8;
+      const uint32_t acc = tmem + uint32_t(j & 1) * 128u;
+      if (j >= 2 && !bd_wait(&bars->dfree[j & 1], ((j >> 1) - 1) & 1, bars, status, 62)) break;
+      tc_fence_after_sync();
+      const uint32_t idesc = tc_idesc_bf16(kBdRows, N);
+      bool ok = true;
+      for (int c = 0; c < nchunks; ++c, ++q) {
+        const uint32_t s = q % n_slots;
+        ok = bd_wait(&bars->full[s], (q / n_slots) & 1, bars, status, 63);
         if (!ok) break;
-        tc_commit(&bars->done[j & 1]);
+        tc_fence_after_sync();
+        const uint32_t sa = smem_u32(ring + size_t(s) * slot_bytes), sb = sa + 8192;
+        const uint64_t da = tc_smem_desc(sa, kBdRows * 16, 128), db = tc_smem_desc(sb, 128, 1024);
+        bd_mma4_warp(acc, da, db, idesc, c > 0);
+        tc_commit_warp(&bars->empty[s], true);
+        tc_commit_warp(&bars->done[j & 1], c == nchunks - 1);
+        __syncwarp();
       }
+      if (!ok) break;
     }
   } else {
     // ---- epilogue warps 0..3

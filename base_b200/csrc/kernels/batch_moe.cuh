@@ -9,7 +9,8 @@
 // tokens is run in passes of 16 (its weights are then served from L2).
 //
 //   moe_expand_digits   f32 rows -> digits, in the order of the routing permutation (an expert's tokens contiguous):
-//                       dig [K block][position][8 digit rows x 16 B], em [position][96] block exponents
+//                       dig [chunk of 8 K blocks][position][K block of the chunk][8 digit rows x 16 B] (the tokens of an
+//                       expert are ONE contiguous piece per chunk), em [position][96] block exponents
 //   moe_batch_mx_*      units = (expert, pass of <= 16 tokens, segment of <= 16 eight-row groups): N <= 128 rows per
 //                       instruction; producer warp (bulk copies: the segment's codes + scale words and the tokens'
 //                       digits of one chunk per ring slot), four scale warps (weights' scale words -> tensor memory),
@@ -78,7 +79,7 @@ moe_expand_digits(const float *__restrict__ x, const int *__restrict__ route, ui
       for (int i = 0; i < 8; ++i) X[i] = 0;
     }
     if (valid) {
-      uint8_t *d = dig + (size_t(kb) * a.P + p) * 128 + sub * 4;
+      uint8_t *d = dig + ((size_t(kb / kBmKc) * a.P + p) * kBmKc + (kb % kBmKc)) * 128 + sub * 4;
 #pragma unroll
       for (int q = 0; q < 8; ++q) {                       // digit q (weight 8^q) is digit row 7 - q
         uint32_t word = 0;
@@ -216,11 +217,9 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
           if (q >= kBmSlots && !bm_wait(&bars->empty[s], ((q / kBmSlots) - 1) & 1, bars, status, 72)) { ui = n_units; break; }
           const int kcc = min(kBmKc, kblocks - c * kBmKc), gb = mxw_group_bytes(kcc);
           uint8_t *dst = ring + size_t(s) * kBmSlotBytes;
-          mbar_expect_tx(&bars->full[s], uint32_t(u.ng * gb + kcc * nt * 128));
+          mbar_expect_tx(&bars->full[s], uint32_t(u.ng * gb + nt * kBmKc * 128));
           bulk_g2s(dst, wexp + mxw_chunk_base(c, kBmKc, R) + size_t(u.g0) * gb, uint32_t(u.ng * gb), &bars->full[s]);
-          for (int kbl = 0; kbl < kcc; ++kbl)
-            bulk_g2s(dst + kBmBBytes + kbl * (kBmTok * 128), dig + (size_t(c * kBmKc + kbl) * a.P + off) * 128, uint32_t(nt * 128),
-                     &bars->full[s]);
+          bulk_g2s(dst + kBmBBytes, dig + (size_t(c) * a.P + off) * (kBmKc * 128), uint32_t(nt * kBmKc * 128), &bars->full[s]);
         }
       }
     }
@@ -271,10 +270,11 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
         const int kcc = min(kBmKc, kblocks - c * kBmKc), gb = mxw_group_bytes(kcc);
         const uint32_t sb = smem_u32(ring + size_t(s) * kBmSlotBytes), sa = sb + kBmBBytes;
         for (int pp = 0; 4 * pp < kcc; ++pp) {
-          const uint64_t da = tc_smem_desc(sa + uint32_t(4 * pp) * (kBmTok * 128), kBmTok * 128, 128);
+          // A in the slot: [token][K block of the chunk][8 digit rows x 16 B]: K blocks 128 B apart, tokens 1 KB apart
+          const uint64_t da = tc_smem_desc(sa + uint32_t(4 * pp) * 128, 128, kBmKc * 128);
           const uint64_t db = tc_smem_desc(sb + uint32_t(4 * pp) * 128, 128, uint32_t(gb));
           bm_mma_pair_warp(tDu, da, db, id0, id2, tSFAu + 4 * uint32_t(c * (kBmKc >> 2) + pp), tSFB + s * 8 + uint32_t(pp) * 4,
-                           !(c == 0 && pp == 0), 4 * pp + 2 < kcc, uint32_t(2 * kBmTok * 128) >> 4, 256u >> 4);
+                           !(c == 0 && pp == 0), 4 * pp + 2 < kcc, 256u >> 4, 256u >> 4);
         }
         tc_commit_warp(&bars->empty[s], true);
         tc_commit_warp(&bars->done[ui & 1], c == nch - 1);
