@@ -146,18 +146,22 @@ B200_DEVICE bool bd_wait(uint64_t *bar, uint32_t parity, BdBars *b, int *status,
 
 // Four K = 16 instructions over one K chunk of 64 (the operands advance by two column groups each: 2 x 64 rows x 16 B
 // of A, 2 x 128 B of B), issued by an elected lane of the converged warp.
-B200_DEVICE void bd_mma4_warp(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool accumulate_first) {
+// The four go to accumulators d_tmem + i * d_step (d_step = 0: one accumulator): with several accumulators the
+// instructions of a chunk do not wait for one another's results, the epilogue adds them up.
+B200_DEVICE void bd_mma4_warp(uint32_t d_tmem, uint32_t d_step, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool accumulate_first) {
   asm volatile(
-      "{\n.reg .pred p, q, e;\n.reg .b64 a1, a2, a3, b1, b2, b3;\n"
+      "{\n.reg .pred p, p1, e;\n.reg .b64 a1, a2, a3, b1, b2, b3;\n.reg .b32 d1, d2, d3;\n"
       "elect.sync _|e, 0xffffffff;\n"
-      "setp.ne.b32 p, %4, 0;\nsetp.eq.b32 q, %4, %4;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "setp.eq.b32 p1, %5, 0;\nor.pred p1, p1, p;\n"          // later instructions accumulate unless they own a fresh accumulator
+      "add.u32 d1, %0, %5;\nadd.u32 d2, d1, %5;\nadd.u32 d3, d2, %5;\n"
       "add.u64 a1, %1, 128;\nadd.u64 a2, %1, 256;\nadd.u64 a3, %1, 384;\n"
       "add.u64 b1, %2, 16;\nadd.u64 b2, %2, 32;\nadd.u64 b3, %2, 48;\n"
       "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, q;\n"
-      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], a2, b2, %3, q;\n"
-      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], a3, b3, %3, q;\n}\n" ::"r"(d_tmem),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(uint32_t(accumulate_first))
+      "@e tcgen05.mma.cta_group::1.kind::f16 [d1], a1, b1, %3, p1;\n"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [d2], a2, b2, %3, p1;\n"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [d3], a3, b3, %3, p1;\n}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(uint32_t(accumulate_first)), "r"(d_step)
       : "memory");
 }
 
@@ -177,6 +181,9 @@ dense_tc_gemm(const uint8_t *__restrict__ Wt, const uint8_t *__restrict__ At, co
   // few rows per CTA (qkv, o-proj): small slots, many of them in flight; many rows (lm_head): 6 slots of 24 KB
   const uint32_t slot_bytes = 8192u + uint32_t(max(1, min(kBdMaxGroups, g_hi - g_lo))) * 1024u;
   const uint32_t n_slots = min(uint32_t(kBdSlots), uint32_t(kBdRingBytes) / slot_bytes);
+  // every CTA reads the same A piece for a given K chunk: start each CTA at a different chunk, so that at any moment
+  // the CTAs ask L2 for different lines (a CTA's own summation order stays fixed)
+  const int c_off = int((blockIdx.x * 7u) % uint32_t(nchunks));
 
   if (tid == 0) {
     for (int i = 0; i < kBdSlots; ++i) { mbar_init(&bars->full[i], 1); mbar_init(&bars->empty[i], 1); }
@@ -184,7 +191,7 @@ dense_tc_gemm(const uint8_t *__restrict__ Wt, const uint8_t *__restrict__ At, co
     bars->abort = 0;
   }
   fence_barrier_init();
-  if (warp == 0) tc_alloc(&bars->tmem_base, 256);
+  if (warp == 0) tc_alloc(&bars->tmem_base, 512);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -204,8 +211,9 @@ dense_tc_gemm(const uint8_t *__restrict__ Wt, const uint8_t *__restrict__ At, co
           if (q >= n_slots && !bd_wait(&bars->empty[s], ((q / n_slots) - 1) & 1, bars, status, 61)) { j = jobs; break; }
           uint8_t *dst = ring + size_t(s) * slot_bytes;
           mbar_expect_tx(&bars->full[s], 8192u + uint32_t(ng) * 1024u);
-          bulk_g2s(dst, At + (size_t(pass) * nchunks + c) * 8192, 8192u, &bars->full[s]);
-          bulk_g2s(dst + 8192, Wt + (size_t(c) * RG + g0) * 1024, uint32_t(ng) * 1024u, &bars->full[s]);
+          const int cc = (c + c_off) % nchunks;
+          bulk_g2s(dst, At + (size_t(pass) * nchunks + cc) * 8192, 8192u, &bars->full[s]);
+          bulk_g2s(dst + 8192, Wt + (size_t(cc) * RG + g0) * 1024, uint32_t(ng) * 1024u, &bars->full[s]);
         }
       }
     }
@@ -215,7 +223,8 @@ dense_tc_gemm(const uint8_t *__restrict__ Wt, const uint8_t *__restrict__ At, co
     for (int j = 0; j < jobs; ++j) {
       const int u = j / passes;
       const int g0 = g_lo + u * kBdMaxGroups, ng = min(kBdMaxGroups, g_hi - g0), N = ng * 8;
-      const uint32_t acc = tmem + uint32_t(j & 1) * 128u;
+      const uint32_t acc = tmem + uint32_t(j & 1) * 256u;
+      const uint32_t d_step = N <= 64 ? 64u : 0u;            // four accumulators of 64 columns, or one of up to 128
       if (j >= 2 && !bd_wait(&bars->dfree[j & 1], ((j >> 1) - 1) & 1, bars, status, 62)) break;
       tc_fence_after_sync();
       const uint32_t idesc = tc_idesc_bf16(kBdRows, N);
@@ -227,7 +236,7 @@ dense_tc_gemm(const uint8_t *__restrict__ Wt, const uint8_t *__restrict__ At, co
         tc_fence_after_sync();
         const uint32_t sa = smem_u32(ring + size_t(s) * slot_bytes), sb = sa + 8192;
         const uint64_t da = tc_smem_desc(sa, kBdRows * 16, 128), db = tc_smem_desc(sb, 128, 1024);
-        bd_mma4_warp(acc, da, db, idesc, c > 0);
+        bd_mma4_warp(acc, d_step, da, db, idesc, c > 0);
         tc_commit_warp(&bars->empty[s], true);
         tc_commit_warp(&bars->done[j & 1], c == nchunks - 1);
         __syncwarp();
@@ -239,13 +248,20 @@ dense_tc_gemm(const uint8_t *__restrict__ Wt, const uint8_t *__restrict__ At, co
     for (int j = 0; j < jobs; ++j) {
       const int u = j / passes, pass = j % passes;
       const int g0 = g_lo + u * kBdMaxGroups, ng = min(kBdMaxGroups, g_hi - g0), N = ng * 8;
-      const uint32_t acc = tmem + uint32_t(j & 1) * 128u;
+      const uint32_t acc = tmem + uint32_t(j & 1) * 256u;
+      const int n_acc = N <= 64 ? 4 : 1;
       if (!bd_wait(&bars->done[j & 1], (j >> 1) & 1, bars, status, 64)) break;
       tc_fence_after_sync();
       const int row = a.m64_rows16 ? (lane < 16 ? warp * 16 + lane : -1) : (warp < 2 ? warp * 32 + lane : -1);
       for (int c0 = 0; c0 < N; c0 += 16) {
         float v[16];
         tc_ld16(acc + (uint32_t(warp * 32) << 16) + uint32_t(c0), v);
+        for (int i = 1; i < n_acc; ++i) {
+          float w[16];
+          tc_ld16(acc + (uint32_t(warp * 32) << 16) + uint32_t(i * 64 + c0), w);
+#pragma unroll
+          for (int q2 = 0; q2 < 16; ++q2) v[q2] += w[q2];
+        }
         if (row >= 0) {
 #pragma unroll
           for (int i = 0; i < 16; ++i) stage[row * kBdStageStride + c0 + i] = v[i];
@@ -271,6 +287,6 @@ dense_tc_gemm(const uint8_t *__restrict__ Wt, const uint8_t *__restrict__ At, co
   __syncthreads();
   if (warp == 0) {
     tc_fence_after_sync();
-    tc_dealloc(tmem, 256);
+    tc_dealloc(tmem, 512);
   }
 }

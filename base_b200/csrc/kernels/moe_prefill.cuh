@@ -266,7 +266,8 @@ moe_prefill_down(const uint4 *__restrict__ tcodes, const uint32_t *__restrict__ 
 // ---- routing for many tokens -----------------------------------------------------------------
 // Router logits: logits[t][e] = Wr[e] . x[t] + br[e] (f32, same fold as moe_router_logits per
 // row: lane-strided float4 walk, xor butterfly).  grid = ceil(T / 4) CTAs of 256 threads: a CTA
-// stages four tokens in shared memory, warp w computes experts w, w + 8, ...
+// stages four tokens in shared memory, warp w computes experts w, w + 8, ... (with grid.y > 1 the experts are
+// divided among grid.y CTAs: many-token callers use grid.y = 1, the batched decode step grid.y = E / 8)
 struct RouterManyArgs { int T, H, E; };
 
 extern "C" __global__ void __launch_bounds__(256)
@@ -279,7 +280,7 @@ moe_router_many(const float *__restrict__ Wr, const float *__restrict__ br, cons
   float4 *xs = reinterpret_cast<float4 *>(dyn_smem);            // [4][H]
   for (int i = tid; i < nt * n4; i += 256) xs[i] = __ldg(reinterpret_cast<const float4 *>(x + size_t(t0) * a.H) + i);
   __syncthreads();
-  for (int e = warp; e < a.E; e += 8) {
+  for (int e = warp + 8 * blockIdx.y; e < a.E; e += 8 * gridDim.y) {      // grid.y CTAs share the experts
     const float4 *w4 = reinterpret_cast<const float4 *>(Wr + size_t(e) * a.H);
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int c = lane; c < n4; c += 32) {
