@@ -393,7 +393,9 @@ def main():
                     help="with --batch > 1 on one GPU: do not also measure the batch-1 persistent kernel")
     ap.add_argument("--repeats", type=int, default=5,
                     help="how many times the K-step timed loop runs; the line reports the median repeat and the spread")
-    ap.add_argument("--workload", choices=("gptoss", "qwen2", "prefill"), default="gptoss",
+    ap.add_argument("--synthetic-kv", action="store_true",
+                    help="batched workloads: start from a seeded synthetic KV cache at the prompt length instead of feeding the prompt")
+    ap.add_argument("--workload", choices=("gptoss", "gptoss120b", "qwen2", "prefill"), default="gptoss",
                     help="gptoss: BASELINE config 3 (the headline); qwen2: BASELINE config 1 (Qwen2-0.5B f32, single GPU); "
                          "prefill: BASELINE config 2 (one MoE layer, 2048 tokens, tensor cores)")
     ap.add_argument("--step", choices=("persistent", "per-op"), default="persistent",
@@ -410,6 +412,14 @@ def main():
         return run_qwen2(a, rank)
     if a.workload == "prefill":
         return run_prefill(a, rank)
+    if a.workload == "gptoss120b":
+        # BASELINE config 4: gpt-oss-120b shapes (36 layers, 128 experts), batch 256, KV context 4096 (synthetic cache)
+        if a.batch == 32:
+            a.batch = 256
+        if a.prompt == PROMPT:
+            a.prompt = 4096
+        a.synthetic_kv = True
+        return run_batched(a, rank, world, local)
     if a.batch > 1:
         return run_batched(a, rank, world, local)
     return run_batch1(a, rank, world, local)
@@ -581,13 +591,19 @@ def run_batched(a, rank: int, world: int, local: int):
     from base_b200.gptoss import GPT_OSS_20B, GptOss, PDL, BATCHED
     from base_b200.dist import Ranks
     Bg = a.batch
-    if Bg % world or GPT_OSS_20B.experts % world:
-        raise SystemExit(f"--batch {Bg} and the {GPT_OSS_20B.experts} experts must be divisible by the {world} GPUs")
+    big = a.workload == "gptoss120b"
+    model = dataclasses.replace(GPT_OSS_20B, layers=36, experts=128) if big else GPT_OSS_20B
+    name = "gpt-oss-120b" if big else "gpt-oss-20b"
+    if Bg % world or model.experts % world:
+        raise SystemExit(f"--batch {Bg} and the {model.experts} experts must be divisible by the {world} GPUs")
     per = Bg // world
     reps = max(1, a.repeats)
-    cfg = dataclasses.replace(GPT_OSS_20B, batch=per, max_seq=a.prompt + a.warmup + (reps + 1) * a.steps + 8,
+    cfg = dataclasses.replace(model, batch=per, max_seq=a.prompt + a.warmup + (reps + 1) * a.steps + 8,
                               flags=PDL | BATCHED, ep_rank=rank, ep_world=world)
-    config = {"workload": f"gpt-oss-20b decode, {Bg} sequences, 2048-token prompts, greedy (BASELINE config 3, batch {Bg})",
+    metric = METRIC.replace("gpt-oss-20b", name)
+    config = {"workload": f"{name} decode, {Bg} sequences, {a.prompt}-token " +
+                          ("contexts (seeded synthetic KV cache)" if a.synthetic_kv else "prompts") +
+                          f", greedy (BASELINE config {'4' if big else '3'}, batch {Bg})",
               "layers": cfg.layers, "hidden": cfg.hidden, "experts": cfg.experts, "top_k": cfg.top_k, "vocab": cfg.vocab,
               "context": a.prompt, "global_batch": Bg, "batch_per_gpu": per,
               "parallelism": (f"expert parallel x{world} (experts {cfg.experts // world} per GPU, NCCL all-gather + all-to-all per "
@@ -597,13 +613,17 @@ def run_batched(a, rank: int, world: int, local: int):
     if a.impl == "reference":
         if rank != 0:
             return
-        one = dataclasses.replace(GPT_OSS_20B, max_seq=a.prompt + a.steps + a.warmup + 8)
-        base, t_step, n_timed = cpu_reference(one, a.prompt, a.steps, a.warmup)
+        one = dataclasses.replace(model, max_seq=a.prompt + a.steps + a.warmup + 8)
+        if big:        # 61 GB of expert weights: the CPU step is composed from a 2-layer model's measured pieces
+            base = cpu_baseline(one, a.prompt)
+            t_step, n_timed = 1.0 / base["value"], 0
+        else:
+            base, t_step, n_timed = cpu_reference(one, a.prompt, a.steps, a.warmup)
         base["sample"] += (f"; the reference decodes one sequence per call (no batching), so {Bg} sequences cost {Bg} such "
                            "steps and its tokens/s does not depend on the batch")
         config = dict(config, step="C port of the reference's CPU path, one sequence and one decode step per call",
                       parallelism=f"{base['cores']} host threads")
-        line = {"metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps,
+        line = {"metric": metric, "value": base["value"], "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps,
                 "steps_timed": n_timed, "warmup": a.warmup, "ms_per_step": t_step * 1e3 * Bg, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "mxfp4 weights, f32 accumulate", "data": "synthetic",
                 "config": config, "impl": "reference", "cpu_baseline": base,
@@ -617,10 +637,14 @@ def run_batched(a, rank: int, world: int, local: int):
     if world > 1:
         m.comm_init(ranks.broadcast_bytes(GptOss.new_comm_id() if rank == 0 else None))
     rng = np.random.default_rng(1000 * 3 + 17)
-    prompt = rng.integers(0, cfg.vocab, size=(a.prompt, Bg))[:, rank * per:(rank + 1) * per]
-    toks = None
-    for pos in range(a.prompt):
-        toks = m.infer(prompt[pos].tolist(), [pos] * per)
+    if a.synthetic_kv:
+        m.fill_kv()
+        toks = rng.integers(0, cfg.vocab, size=Bg)[rank * per:(rank + 1) * per]
+    else:
+        prompt = rng.integers(0, cfg.vocab, size=(a.prompt, Bg))[:, rank * per:(rank + 1) * per]
+        toks = None
+        for pos in range(a.prompt):
+            toks = m.infer(prompt[pos].tolist(), [pos] * per)
     toks, pos = [int(t) for t in toks], a.prompt
     m.prep(toks, [pos] * per)
     if a.warmup:
@@ -680,7 +704,7 @@ def run_batched(a, rank: int, world: int, local: int):
                               "attn_decode_batch": {"us_per_launch": per_launch(at_ms) * 1e6}},
             "whole_step": {"bytes_per_gpu": step_bytes, "achieved": step_bytes / step_s / 1e9, "frac": step_bytes / step_s / 1e9 / peak}}
     launches_per_step = 1 + cfg.layers * 14 + 3
-    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup,
+    line = {"metric": metric, "value": value, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup,
             "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "mxfp4 experts / bf16 dense weights, f32 accumulate", "data": "synthetic", "config": config,
             "e2e": {"value": Bg * a.steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 8 * per, "d2h_bytes_per_step": 4 * per},
@@ -688,13 +712,13 @@ def run_batched(a, rank: int, world: int, local: int):
             "repeats": {"n": len(rep_ms), "ms_per_step": [round(r / a.steps, 5) for r in rep_ms], "reported": "median",
                         "min_tokens_per_s": Bg * a.steps / (max(rep_ms) * 1e-3), "max_tokens_per_s": Bg * a.steps / (min(rep_ms) * 1e-3)}}
     m.close()
-    if world == 1 and not a.no_batch1:
+    if world == 1 and not a.no_batch1 and not big:
         # the batch-1 workload of the same config on the same GPU: the persistent step kernel
         b1 = run_batch1(a, rank, world, local, ranks=ranks, emit=False)
         line["batch1"] = {k: b1[k] for k in ("value", "ms_per_step", "e2e", "roofline", "repeats", "gpu_launches")}
         line["batch1"]["config"] = b1["config"]
     if rank == 0:
-        line["cpu_baseline"] = cpu_baseline(dataclasses.replace(GPT_OSS_20B), a.prompt)
+        line["cpu_baseline"] = cpu_baseline(dataclasses.replace(model), a.prompt)
         print(json.dumps(line))
     ranks.close()
 
