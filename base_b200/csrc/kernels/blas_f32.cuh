@@ -117,26 +117,37 @@ sgemm_naive_f32(const float *__restrict__ A, const float *__restrict__ B, float 
   c[size_t(j) * g.ldc + i] = v;
 }
 
-// Streaming read probe: every CTA sums a contiguous slice with 16-byte loads
-// (unroll 8) and writes one float.  Used to measure what HBM delivers for a
-// transfer of a given size (the practical roofline of the small GEMVs).
-struct ReadProbeArgs { unsigned long long offset_vec; unsigned long long n_vec; };
+// ---- GEMV in the reference's committed fold order ---------------------------------------------------
+// y[r] = W[r] . x with ONE warp per output row and the reference's own arithmetic, so that the result is
+// bit-identical to the reference's CPU image of its kernels (applications/warp-check/src/lib.rs:28-116,
+// lean/lib/AlgorithmLib/ML/Sched.lean:7-64, ML/Schema.lean:10-44): per lane a sequential walk
+// acc = acc + (a * b) with separate multiply and add, then the xor butterfly 16, 8, 4, 2, 1
+// (lane = lane + other), result read at lane 0.  walk 0 = vec4 (four contiguous elements per lane per
+// trip, the warp strides by 128; needs cols % 128 == 0), 1 = strided (one element per lane per trip, stride
+// 32; cols % 32 == 0), 2 = blocked (lane l walks the run l * cols / 32 ...).  For checks and for callers that
+// need the reference's bits; the fused kernels above are the fast path.
+struct WarpFoldArgs { int rows, cols, walk; };
 
 extern "C" __global__ void __launch_bounds__(256)
-read_probe(const uint4 *__restrict__ src, float *__restrict__ sink, ReadProbeArgs a) {
-  pdl_wait();
-  pdl_launch_dependents();
-  const uint4 *p = src + a.offset_vec;
-  const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
-  unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
-  uint32_t acc = 0;
-  for (; i + 7 * stride < a.n_vec; i += 8 * stride) {
-    uint4 v[8];
+gemv_warp_fold_f32(const float *__restrict__ W, const float *__restrict__ x, float *__restrict__ y, WarpFoldArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= a.rows) return;
+  const float *w = W + size_t(row) * a.cols;
+  float acc = 0.f;
+  if (a.walk == 0) {
+    for (int t = 0; t < a.cols / 128; ++t) {
+      const int o = t * 128 + lane * 4;
 #pragma unroll
-    for (int u = 0; u < 8; ++u) v[u] = __ldcs(p + i + u * stride);
-#pragma unroll
-    for (int u = 0; u < 8; ++u) acc ^= v[u].x ^ v[u].y ^ v[u].z ^ v[u].w;
+      for (int q = 0; q < 4; ++q) acc = __fadd_rn(acc, __fmul_rn(w[o + q], x[o + q]));
+    }
+  } else if (a.walk == 1) {
+    for (int t = 0; t < a.cols / 32; ++t) acc = __fadd_rn(acc, __fmul_rn(w[t * 32 + lane], x[t * 32 + lane]));
+  } else {
+    const int run = a.cols / 32;
+    for (int t = 0; t < run; ++t) acc = __fadd_rn(acc, __fmul_rn(w[lane * run + t], x[lane * run + t]));
   }
-  for (; i < a.n_vec; i += stride) { const uint4 v = __ldcs(p + i); acc ^= v.x ^ v.y ^ v.z ^ v.w; }
-  if (acc == 0x12345678u) sink[blockIdx.x] = 1.f;
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, m));
+  if (lane == 0) y[row] = acc;
 }

@@ -128,10 +128,3 @@ B200_DEVICE float silu(float g) { return g / (1.0f + __expf(-g)); }
 // ---- programmatic dependent launch --------------------------------------------
 B200_DEVICE void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 B200_DEVICE void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
-// Empty kernel: measures launch and dependency latency (cl_b200_launch tests).
-extern "C" __global__ void noop_kernel(int *sink) {
-  pdl_wait();
-  pdl_launch_dependents();
-  if (sink && threadIdx.x == 1024) *sink = 0;
-}

@@ -24,7 +24,6 @@
 #pragma once
 #include "tc_gemm.cuh"
 
-constexpr int kMxTermsMax = 16;
 
 // Instruction descriptor of kind::mxf4: E2M1 x E2M1, UE8M0 scales, K-major operands, f32 accumulator.
 B200_DEVICE uint32_t mx_idesc(int M, int N, uint32_t a_sf_byte, uint32_t b_sf_byte) {
@@ -101,199 +100,4 @@ B200_DEVICE uint32_t f32x2_to_e2m1x2(float lo, float hi) {
   uint32_t r;
   asm("{\n.reg .b8 b;\ncvt.rn.satfinite.e2m1x2.f32 b, %1, %2;\ncvt.u32.u8 %0, b;\n}\n" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
-}
-
-// ---- activation expansion -----------------------------------------------------------------------
-// One 32-element block of K is handled by four consecutive lanes, 8 elements each.  Term t:
-//   m = largest |residual| of the block; scale = 2^(exponent(m) - 1), so residual / scale is in (-4, 4)
-//   where E2M1 is spaced by at most 1: the new residual is at most m / 4.
-// Whole warps call this (the block maximum is a shuffle); `valid` guards the stores.
-// a_tile: A operand, [K / 32][2 row groups][8 rows][16 B]; sfa: [K / 128][32 rows][16 B], bytes 0..3 of a row used.
-B200_DEVICE void mx_expand_block(float (&r)[8], int terms, uint8_t *a_tile, uint8_t *sfa, int kb, int sub, bool valid) {
-#pragma unroll 1
-  for (int t = 0; t < terms; ++t) {
-    float m = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(r[i]));
-    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-    const uint32_t em = (__float_as_uint(m) >> 23) & 0xffu;      // biased exponent of the block maximum
-    uint32_t word = 0, sbyte = 127;
-    if (em >= 2 && em < 255) {
-      sbyte = em - 1;
-      const float inv = __uint_as_float((254u - sbyte) << 23);   // 2^-(sbyte - 127)
-      const float sc = __uint_as_float(sbyte << 23);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) word |= f32x2_to_e2m1x2(r[2 * i] * inv, r[2 * i + 1] * inv) << (8 * i);
-      float q[8];
-      e2m1x8_to_f32(word, q);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) r[i] = fmaf(-q[i], sc, r[i]);
-    }
-    if (valid) *reinterpret_cast<uint32_t *>(a_tile + size_t(kb) * 256 + (t >> 3) * 128 + (t & 7) * 16 + sub * 4) = word;
-    if (valid && sub == 0) sfa[(kb >> 2) * 512 + t * 16 + (kb & 3)] = uint8_t(sbyte);
-  }
-}
-
-// ---- test kernel: y[n] = sum_k dequant(W)[n][k] x[k] for 32 rows per CTA -------------------------
-// codes [rows][K / 2] (element 2i in the low nibble), scales [rows][K / 32] (UE8M0), x [K] f32.
-// Scale columns in tensor memory, for both operands: one 4-column group per 4 K blocks (column 0 of the
-// group = rows 0..31, its bytes = the 4 K blocks).  The scale address of an instruction has to be a
-// multiple of 4 columns (anything else is rejected as a misaligned address), also when the operand has
-// only 32 rows and so uses one column of the group.
-struct MxGemvArgs { int K, terms; };     // K % 32 == 0, K <= 4096; 1 <= terms <= 16
-
-extern "C" __global__ void __launch_bounds__(128)
-mxf4_tc_gemv_test(const uint8_t *__restrict__ codes, const uint8_t *__restrict__ scales, const float *__restrict__ x,
-                  float *__restrict__ y, int *__restrict__ status, MxGemvArgs a) {
-  const int K = a.K, kblocks = K >> 5, atoms = (kblocks + 3) >> 2, steps = (kblocks + 1) >> 1;
-  uint8_t *sA = dyn_smem;                                   // kblocks * 256 (+ 14 * 128: rows the tensor core reads beyond the data)
-  uint8_t *sSFA = sA + kblocks * 256 + 2048;                // atoms * 512
-  uint8_t *sB = sSFA + atoms * 512;                         // kblocks * 512 (32 rows = 4 row groups)
-  uint8_t *sSFB = sB + (kblocks + 1) * 512;                 // atoms * 512
-  __shared__ uint64_t done_bar;
-  __shared__ uint32_t tmem_base;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int row0 = blockIdx.x * 32;
-
-  if (tid == 0) mbar_init(&done_bar, 1);
-  fence_barrier_init();
-  if (warp == 0) tc_alloc(&tmem_base, 512);
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem = tmem_base;
-  const uint32_t tD = tmem, tSFA = tmem + 64, tSFB = tmem + 256;       // columns: 32 accumulator, 4 * atoms each for the scales
-
-  // what is read but not written below: unused scale bytes = 1.0, the odd last K block, the tail of sA
-  for (int i = tid; i < (atoms * 512) / 4; i += 128) {
-    reinterpret_cast<uint32_t *>(sSFA)[i] = 0x7f7f7f7fu;
-    reinterpret_cast<uint32_t *>(sSFB)[i] = 0x7f7f7f7fu;
-  }
-  for (int i = tid; i < 2048 / 4; i += 128) reinterpret_cast<uint32_t *>(sA + kblocks * 256)[i] = 0;
-  for (int i = tid; i < 512 / 4; i += 128) reinterpret_cast<uint32_t *>(sB + kblocks * 512)[i] = 0;
-  __syncthreads();
-
-  // ---- A: expand x (scales: [K block / 4][32 lanes][16 B], bytes 0..3 of a lane = its 4 K blocks)
-  for (int kb0 = 0; kb0 < kblocks; kb0 += 32) {
-    float r[8];
-    const int kb = kb0 + (tid >> 2), sub = tid & 3;
-    const bool valid = kb < kblocks;
-    const float4 v0 = valid ? *reinterpret_cast<const float4 *>(x + kb * 32 + sub * 8) : make_float4(0.f, 0.f, 0.f, 0.f);
-    const float4 v1 = valid ? *reinterpret_cast<const float4 *>(x + kb * 32 + sub * 8 + 4) : make_float4(0.f, 0.f, 0.f, 0.f);
-    r[0] = v0.x; r[1] = v0.y; r[2] = v0.z; r[3] = v0.w; r[4] = v1.x; r[5] = v1.y; r[6] = v1.z; r[7] = v1.w;
-    mx_expand_block(r, a.terms, sA, sSFA, kb, sub, valid);
-  }
-  // rows terms..15 of A: zero codes (their sums are dropped anyway, but keep them finite)
-  for (int i = tid; i < kblocks * 16; i += 128) {
-    const int kb = i >> 4, t = i & 15;
-    if (t >= a.terms) {
-      uint4 *p = reinterpret_cast<uint4 *>(sA + size_t(kb) * 256 + (t >> 3) * 128 + (t & 7) * 16);
-      *p = make_uint4(0, 0, 0, 0);
-    }
-  }
-  // ---- B: 32 weight rows, [K block][4 row groups][8 rows][16 B]
-  for (int i = tid; i < kblocks * 32; i += 128) {
-    const int kb = i >> 5, n = i & 31;
-    *reinterpret_cast<uint4 *>(sB + size_t(kb) * 512 + (n >> 3) * 128 + (n & 7) * 16) =
-        *reinterpret_cast<const uint4 *>(codes + size_t(row0 + n) * (K >> 1) + kb * 16);
-    const uint8_t sb = scales[size_t(row0 + n) * kblocks + kb];
-    sSFB[(kb >> 2) * 512 + n * 16 + (kb & 3)] = sb;
-  }
-  fence_async_smem();
-  __syncthreads();
-
-  bool ok = true;
-  if (tid == 0) {
-    tc_fence_after_sync();
-    for (int q = 0; q < atoms; ++q) tc_cp_32x128b(tSFA + 4 * q, smem_u32(sSFA) + q * 512);
-    for (int q = 0; q < atoms; ++q) tc_cp_32x128b(tSFB + 4 * q, smem_u32(sSFB) + q * 512);
-    for (int j = 0; j < steps; ++j) {                       // K elements 64 j .. 64 j + 63 = K blocks 2 j, 2 j + 1
-      const uint32_t kb = uint32_t(2 * j), byte = kb & 3;
-      const uint32_t col = 4 * (kb >> 2);
-      const uint64_t da = tc_smem_desc(smem_u32(sA) + j * 2 * 256, 256, 128);
-      const uint64_t db = tc_smem_desc(smem_u32(sB) + j * 2 * 512, 512, 128);
-      mx_mma(tD, da, db, mx_idesc(128, 32, byte, byte), tSFA + col, tSFB + col, j > 0);
-    }
-    tc_commit(&done_bar);
-  }
-  ok = __syncthreads_and(tc_wait(&done_bar, 0));
-  if (!ok && tid == 0) atomicExch(status, 41);
-  tc_fence_after_sync();
-  if (ok && warp == 0) {
-    // lanes 0..terms-1 hold D[t][0..31]; add them up across the lanes
-    float v[16], w[16];
-    tc_ld16(tD, v);
-    tc_ld16(tD + 16, w);
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      float s0 = lane < a.terms ? v[j] : 0.f, s1 = lane < a.terms ? w[j] : 0.f;
-      s0 = warp_sum(s0);
-      s1 = warp_sum(s1);
-      if (lane == 0) { y[row0 + j] = s0; y[row0 + 16 + j] = s1; }
-    }
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 0) tc_dealloc(tmem, 512);
-}
-
-// ---- issue-rate probe: `reps` block-scaled instructions of shape 128 x N x 64 from one thread per CTA ----
-// Operands and scales are whatever the shared and tensor memory hold (the values do not matter
-// for the time); out[cta] = clock cycles from the first issue to the completion of the last.
-struct MxRateArgs { int N, reps, accs, lbo_a, sbo_a, lbo_b, sbo_b, vary; };     // N in {8, 16, ..., 256}; accs (1, 2, 4 or 8; accs * N <= 256)
-                                                                      // accumulators taken in turn; operand strides in bytes (0: compact);
-                                                                      // vary bit 0/1/2: the A address / B address / scale columns change with every instruction,
-                                                                      // bit 3: the scale byte pair alternates between 0,1 and 2,3; bit 4: accumulator at column 288, scales at
-                                                                      // columns 0 and 96, A tile 176 KB into shared memory (needs 190 KB of it)
-
-extern "C" __global__ void __launch_bounds__(128)
-mxf4_tc_rate_probe(long long *__restrict__ out, int *__restrict__ status, MxRateArgs a) {
-  uint8_t *sS = dyn_smem;                      // 512 B of scale bytes
-  uint8_t *sA = dyn_smem + 512;                // 128 rows x 32 B
-  uint8_t *sB = dyn_smem + 4608;               // N rows x 32 B; dynamic shared memory = 4608 + 32 N bytes (more for wide strides)
-  __shared__ uint64_t done_bar;
-  __shared__ uint32_t tmem_base;
-  const int tid = threadIdx.x, warp = tid >> 5;
-  if (tid == 0) mbar_init(&done_bar, 1);
-  fence_barrier_init();
-  if (warp == 0) tc_alloc(&tmem_base, 512);
-  for (int i = tid; i < (4608 + a.N * 32) / 4; i += 128) reinterpret_cast<uint32_t *>(dyn_smem)[i] = 0x22222222u;   // all codes = 1.0
-  fence_async_smem();
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem = tmem_base;
-  long long t0 = 0, t1 = 0;
-  if (tid == 0) {
-    // scale columns 256.. of tensor memory: 1.0 everywhere
-    for (int i = 0; i < 128; ++i) reinterpret_cast<uint32_t *>(sS)[i] = 0x7f7f7f7fu;
-    fence_async_smem();
-    for (int i = 0; i < 32; ++i) tc_cp_32x128b(tmem + 256 + 4 * i, smem_u32(sS));       // scale columns 256..383: 1.0
-    const uint64_t da = tc_smem_desc(smem_u32(sA), a.lbo_a ? a.lbo_a : 2048, a.sbo_a ? a.sbo_a : 128);
-    const uint64_t db = tc_smem_desc(smem_u32(sB), a.lbo_b ? a.lbo_b : uint32_t(a.N) * 16, a.sbo_b ? a.sbo_b : 128);
-    const uint32_t idesc = mx_idesc(128, a.N, 0, 0), idesc2 = mx_idesc(128, a.N, 2, 2);
-    const bool placed = (a.vary & 16) != 0;       // the step kernel's placement of everything
-    const uint32_t dcol = placed ? 288u : 0u, sfa0 = placed ? 0u : 256u, sfb0 = placed ? 96u : 320u;
-    const uint64_t da_p = placed ? tc_smem_desc(smem_u32(dyn_smem) + 180224u, a.lbo_a ? a.lbo_a : 2048, a.sbo_a ? a.sbo_a : 128) : da;
-    if (placed)
-      for (int i = 0; i < 48; ++i) tc_cp_32x128b(tmem + 4 * i, smem_u32(sS));       // scale columns 0..191: 1.0
-    t0 = clock64();
-    for (int r = 0; r < a.reps; ++r) {
-      const uint32_t k = uint32_t(r & 7);
-      mx_mma(tmem + dcol + uint32_t((r & (a.accs - 1)) * a.N), da_p + ((a.vary & 1) ? 16 * k : 0), db + ((a.vary & 2) ? 16 * k : 0),
-             ((a.vary & 8) && (r & 1)) ? idesc2 : idesc,
-             tmem + sfa0 + ((a.vary & 4) ? 8 * k : 0), tmem + sfb0 + ((a.vary & 4) ? 8 * k : 0), r >= a.accs);
-    }
-    tc_commit(&done_bar);
-  }
-  const bool ok = __syncthreads_and(tc_wait(&done_bar, 0));
-  if (tid == 0) {
-    t1 = clock64();
-    out[blockIdx.x] = t1 - t0;
-    if (!ok) atomicExch(status, 42);
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 0) tc_dealloc(tmem, 512);
 }

@@ -1,6 +1,7 @@
-// 5th-generation tensor-core (tcgen05) building blocks for sm_100a, and a
-// small bf16 GEMM that exercises them: D[128 x N] (f32, in tensor memory) =
-// A[128 x K] (bf16, K-major in shared memory) x B[N x K]^T (bf16, K-major).
+// 5th-generation tensor-core (tcgen05) building blocks for sm_100a:
+// D[128 x N] (f32, in tensor memory) = A[128 x K] (bf16, K-major in shared
+// memory) x B[N x K]^T (bf16, K-major).  A one-CTA GEMM that exercises them
+// lives with the tests (tests/kernels/probe_kernels.cu).
 //
 // What is used:
 //   * tensor memory (TMEM): allocated by one warp (tcgen05.alloc), accumulator
@@ -88,76 +89,3 @@ B200_DEVICE bool tc_wait(uint64_t *bar, uint32_t parity) {
 // ---- operand staging ---------------------------------------------------------------------------
 // Byte offset of element (row r, column c) of an R-row x 64-column bf16 tile in the layout above.
 B200_DEVICE uint32_t tc_tile_off(int R, int r, int c) { return uint32_t(c >> 3) * uint32_t(R) * 16 + uint32_t(r) * 16 + uint32_t(c & 7) * 2; }
-
-// ---- test GEMM: one CTA, C[128][N] = A[128][K] B[N][K]^T ------------------------------------------
-struct TcGemmArgs { int N, K; };     // N in {16, 32, ..., 256}, K % 64 == 0
-
-extern "C" __global__ void __launch_bounds__(128)
-tc_gemm_test(const uint16_t *__restrict__ A, const uint16_t *__restrict__ B, float *__restrict__ C,
-             int *__restrict__ status, TcGemmArgs a) {
-  uint8_t *sA = dyn_smem;                       // 128 x 64 bf16 = 16 KB
-  uint8_t *sB = dyn_smem + 16384;               // up to 256 x 64 bf16 = 32 KB
-  __shared__ uint64_t done_bar;
-  __shared__ uint32_t tmem_base;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int N = a.N, K = a.K;
-  uint32_t ncols = 32;
-  while (ncols < uint32_t(N)) ncols <<= 1;
-
-  if (tid == 0) mbar_init(&done_bar, 1);
-  fence_barrier_init();
-  if (warp == 0) tc_alloc(&tmem_base, ncols);
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem = tmem_base;
-  const uint32_t idesc = tc_idesc_bf16(128, N);
-  bool ok = true;
-
-  for (int k0 = 0, it = 0; k0 < K; k0 += 64, ++it) {
-    // stage A[128][k0..k0+64) and B[N][k0..k0+64): 16-byte vectors (8 bf16), generic-proxy stores
-    for (int i = tid; i < 128 * 8; i += 128) {
-      const int r = i >> 3, cg = i & 7;
-      *reinterpret_cast<uint4 *>(sA + tc_tile_off(128, r, cg * 8)) =
-          *reinterpret_cast<const uint4 *>(A + size_t(r) * K + k0 + cg * 8);
-    }
-    for (int i = tid; i < N * 8; i += 128) {
-      const int r = i >> 3, cg = i & 7;
-      *reinterpret_cast<uint4 *>(sB + tc_tile_off(N, r, cg * 8)) =
-          *reinterpret_cast<const uint4 *>(B + size_t(r) * K + k0 + cg * 8);
-    }
-    fence_async_smem();                         // make the stores visible to the tensor core's reads
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after_sync();
-#pragma unroll
-      for (int s = 0; s < 4; ++s) {             // four K = 16 steps: two column groups each
-        const uint64_t da = tc_smem_desc(smem_u32(sA) + s * 2 * 128 * 16, 128 * 16, 128);
-        const uint64_t db = tc_smem_desc(smem_u32(sB) + s * 2 * N * 16, N * 16, 128);
-        tc_mma_bf16(tmem, da, db, idesc, it > 0 || s > 0);
-      }
-      tc_commit(&done_bar);
-    }
-    // single-buffered: wait until the MMAs have read the tiles before overwriting them
-    ok = __syncthreads_and(tc_wait(&done_bar, it & 1));     // the same verdict for every thread
-    if (!ok) {
-      if (tid == 0) atomicExch(status, 31);
-      break;
-    }
-  }
-
-  tc_fence_after_sync();
-  if (ok) {
-    // warp w reads accumulator rows 32 w .. 32 w + 31 (TMEM lanes), 16 columns at a time
-    const int row = warp * 32 + lane;
-    for (int c0 = 0; c0 < N; c0 += 16) {
-      float v[16];
-      tc_ld16(tmem + (uint32_t(warp * 32) << 16) + uint32_t(c0), v);
-#pragma unroll
-      for (int j = 0; j < 16; ++j) C[size_t(row) * N + c0 + j] = v[j];
-    }
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 0) tc_dealloc(tmem, ncols);
-}

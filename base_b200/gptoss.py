@@ -195,13 +195,6 @@ class GptOss:
         self.base.execute_into(self.art.extras["fetchDequant"], struct.pack("<5I", layer, which, expert, row0, nrows), out)
         return np.frombuffer(bytes(out), dtype="<f4").reshape(nrows, K)
 
-    def bench_moe(self, iters: int = 1, which: int = 0) -> float:
-        """Milliseconds (device events) for `iters` passes over every layer's
-        expert kernels (which: 0 both, 1 gate_up only, 2 down only)."""
-        out = bytearray(4)
-        self.base.execute_into(self.art.extras["benchMoe"], struct.pack("<2I", iters, which), out)
-        return struct.unpack("<f", bytes(out))[0]
-
     BATCH_KERNELS = dict(gate_up=1, down=2, qkv=3, o_proj=4, attention=5, lm_head=6)
 
     def bench_batch(self, which: str, iters: int = 1) -> float:

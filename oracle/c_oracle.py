@@ -144,3 +144,12 @@ def rowdot_gemv(W: np.ndarray, x: np.ndarray, threads: int = 1) -> np.ndarray:
     y = np.empty(W.shape[0], dtype=np.float32)
     lib().oracle_rowdot_gemv_f32(_p(W), _p(x), _p(y), W.shape[0], W.shape[1], threads)
     return y
+
+
+def warp_fold_gemv(W: np.ndarray, x: np.ndarray, walk: int) -> np.ndarray:
+    """The reference's committed warp fold (applications/warp-check/src/lib.rs:28-116) over W [rows][n] f32."""
+    W = np.ascontiguousarray(W, dtype=np.float32)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    y = np.empty(W.shape[0], dtype=np.float32)
+    lib().oracle_warp_fold_gemv(_p(W), _p(x), _p(y), W.shape[0], W.shape[1], walk)
+    return y

@@ -141,6 +141,31 @@ void oracle_rowdot_gemv_f32(const float *W, const float *x, float *y, int rows, 
   gemv_f32(W, x, NULL, y, rows, K);
 }
 
+/* The reference's committed GPU fold, its own CPU image (applications/warp-check/src/lib.rs:28-116: `butterfly`,
+ * `Walk::idx`, `dot_by`): 32 lane accumulators walk the row (walk 0 vec4, 1 strided, 2 blocked), acc += a * b with
+ * separate multiply and add, then five xor rounds lane[l] = prev[l] + prev[l ^ m], m = 16, 8, 4, 2, 1, read at lane 0. */
+void oracle_warp_fold_gemv(const float *W, const float *x, float *y, int rows, int n, int walk) {
+#pragma omp parallel for schedule(static)
+  for (int r = 0; r < rows; ++r) {
+    const float *w = W + (size_t)r * n;
+    float lane[32], prev[32];
+    const int trips = walk == 0 ? n / 128 : n / 32, width = walk == 0 ? 4 : 1;
+    for (int l = 0; l < 32; ++l) {
+      float acc = 0.0f;
+      for (int t = 0; t < trips; ++t) {
+        const int o = walk == 0 ? t * 128 + l * 4 : walk == 1 ? t * 32 + l : l * (n / 32) + t;
+        for (int q = 0; q < width; ++q) acc = acc + w[o + q] * x[o + q];
+      }
+      lane[l] = acc;
+    }
+    for (int m = 16; m > 0; m >>= 1) {
+      memcpy(prev, lane, sizeof(lane));
+      for (int l = 0; l < 32; ++l) lane[l] = prev[l] + prev[l ^ m];
+    }
+    y[r] = lane[0];
+  }
+}
+
 static void rms_norm(const float *g, const float *x, float *y, int n, float eps) {
   float ss = 0.0f;
   for (int i = 0; i < n; ++i) ss = ss + x[i] * x[i];

@@ -44,3 +44,20 @@ def pytest_collection_modifyitems(config, items):
 @pytest.fixture(scope="session")
 def golden():
     return GOLDEN
+
+
+def build_probe_kernels() -> Path:
+    """Compile tests/kernels/probe_kernels.cu (test and probe kernels, not part of the library's image) to a cubin
+    next to it; nvcc cross-compiles, so this also runs on a host without a GPU."""
+    import subprocess
+    src = Path(__file__).resolve().parent / "kernels" / "probe_kernels.cu"
+    out = src.parent / "_build" / "probe_kernels.cubin"
+    inc = ROOT / "base_b200" / "csrc" / "kernels"
+    deps = [src] + list(inc.glob("*.cuh"))
+    if not out.exists() or any(d.stat().st_mtime > out.stat().st_mtime for d in deps):
+        out.parent.mkdir(exist_ok=True)
+        nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+        subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-cubin", "-O3", "-lineinfo", "-std=c++17",
+                        "-I", str(inc), "-o", str(out), str(src)], check=True)
+    return out
+

@@ -251,3 +251,37 @@ def test_builtin_module_and_b200_launch_checks(ctx):
     assert L.cl_b200_memset_async(c, buf, 60, 0, 8, -1) == -1
     assert L.cl_cuda_sync(c) == 0
     assert np.all(down(L, c, buf, 64, np.uint8) == 0xAB)
+
+
+@pytest.mark.parametrize("n,m", [(896, 4864), (2048, 4096), (8192, 2048), (16384, 2048)])
+def test_committed_fold_gemv_is_bit_exact_on_the_reference_inputs(n, m):
+    """The reference checks its proven GEMV kernels bit for bit against a CPU fold written in the committed order
+    (applications/gemv-warp/src/main.rs:55-56, 129-148, 184-189: a[i] = ((i % 251) - 125) * 1e-3,
+    x[i] = ((i % 97) - 48) * 1e-2, these four shapes).  `gemv_warp_fold_f32` commits to the same order; the oracle
+    restates the reference's CPU image (applications/warp-check/src/lib.rs:28-116)."""
+    import ctypes
+    import struct
+    from base_b200 import lib
+    from oracle import c_oracle
+    L = lib()
+    slot = ctypes.c_void_p(0)
+    L.cl_cuda_init(ctypes.byref(slot))
+    assert slot.value
+    c = slot
+    i = np.arange(m * n, dtype=np.int64)
+    a = (((i % 251).astype(np.float32) - np.float32(125.0)) * np.float32(0.001)).astype(np.float32).reshape(m, n)
+    x = (((np.arange(n) % 97).astype(np.float32) - np.float32(48.0)) * np.float32(0.01)).astype(np.float32)
+    mod = L.cl_b200_builtin_module(c)
+    ba, bx, by = (L.cl_cuda_create_buffer(c, a.nbytes), L.cl_cuda_create_buffer(c, x.nbytes), L.cl_cuda_create_buffer(c, m * 4))
+    assert L.cl_cuda_upload_ptr(c, ba, a.ctypes.data_as(ctypes.c_void_p), a.nbytes) == 0
+    assert L.cl_cuda_upload_ptr(c, bx, x.ctypes.data_as(ctypes.c_void_p), x.nbytes) == 0
+    for walk in (0, 1, 2):                                   # vec4, strided, blocked
+        args = struct.pack("<3i", m, n, walk)
+        assert L.cl_b200_launch(c, mod, b"gemv_warp_fold_f32", 3, struct.pack("<3i", ba, bx, by), args, len(args),
+                                (m + 7) // 8, 1, 1, 256, 1, 1, 0, -1, 0) == 0
+        assert L.cl_cuda_sync(c) == 0
+        y = np.zeros(m, dtype=np.float32)
+        assert L.cl_cuda_download_ptr(c, by, y.ctypes.data_as(ctypes.c_void_p), y.nbytes) == 0
+        want = c_oracle.warp_fold_gemv(a, x, walk)
+        np.testing.assert_array_equal(y.view(np.uint32), want.view(np.uint32), err_msg=f"walk {walk}")
+    L.cl_cuda_cleanup(ctypes.byref(slot))

@@ -14,6 +14,16 @@ from oracle import moe_oracle
 pytestmark = [pytest.mark.gpu, pytest.mark.timeout(120, method="thread")]
 
 
+def load_probe_module(L, c):
+    """The test/probe kernels live in their own cubin (tests/kernels/probe_kernels.cu), not in the library's image."""
+    from conftest import build_probe_kernels
+    image = build_probe_kernels().read_bytes()
+    buf = ctypes.create_string_buffer(image, len(image))
+    m = L.cl_b200_load_module(c, ctypes.cast(buf, ctypes.c_void_p), len(image))
+    assert m >= 0, L.cl_b200_last_error().decode()
+    return m
+
+
 @pytest.fixture()
 def ctx():
     L = lib()
@@ -27,7 +37,7 @@ def ctx():
 def run_gemv(L, c, codes, scales, x, terms):
     rows, K = codes.shape[0], codes.shape[1] * 2
     kblocks, atoms = K // 32, (K // 32 + 3) // 4
-    m = L.cl_b200_builtin_module(c)
+    m = load_probe_module(L, c)
     ins = [np.ascontiguousarray(codes), np.ascontiguousarray(scales), np.ascontiguousarray(x, dtype=np.float32)]
     bufs = [L.cl_cuda_create_buffer(c, a.nbytes) for a in ins] + [L.cl_cuda_create_buffer(c, rows * 4),
                                                                    L.cl_cuda_create_buffer(c, 4)]
@@ -70,7 +80,7 @@ def test_block_scaled_mxfp4_gemv_matches_dequantised_product(ctx, rows, K, terms
 def test_issue_rate_probe_runs(ctx):
     """The rate probe (bench material) completes and reports a positive cycle count per CTA."""
     L, c = ctx
-    m = L.cl_b200_builtin_module(c)
+    m = load_probe_module(L, c)
     bufs = [L.cl_cuda_create_buffer(c, 8 * 4), L.cl_cuda_create_buffer(c, 4)]
     bind = struct.pack("<2i", *bufs)
     args = struct.pack("<8i", 32, 64, 2, 0, 0, 0, 0, 7)

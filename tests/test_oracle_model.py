@@ -159,3 +159,21 @@ def test_rowdot_fold_is_the_reference_cpu_gemv_order():
         got = c_oracle.rowdot_gemv(W, x, threads=1)
         np.testing.assert_array_equal(got.view(np.uint32), want.view(np.uint32))
         np.testing.assert_array_equal(c_oracle.rowdot_gemv(W, x, threads=3).view(np.uint32), want.view(np.uint32))
+
+
+def test_warp_fold_restatement_matches_the_reference_unit_tests():
+    # applications/warp-check/src/lib.rs:260-281: the three walks cover the same indices (the folds agree on
+    # exactly representable data) and the butterfly sums 32 ones to 32
+    from oracle import c_oracle
+    ones = np.ones((1, 256), dtype=np.float32)
+    for walk in (0, 1, 2):
+        assert c_oracle.warp_fold_gemv(ones, ones[0], walk)[0] == 256.0
+    a = (np.arange(3 * 1024) % 7).astype(np.float32).reshape(3, 1024)
+    x = (np.arange(1024) % 5).astype(np.float32)
+    want = (a.astype(np.float64) @ x.astype(np.float64)).astype(np.float32)
+    for walk in (0, 1, 2):
+        np.testing.assert_array_equal(c_oracle.warp_fold_gemv(a, x, walk), want)     # small integers: every order is exact
+    # and on data that is not exactly summable the walks differ in the last bits, as the reference says they do
+    r = np.random.default_rng(0)
+    b, z = r.standard_normal((4, 4096)).astype(np.float32), r.standard_normal(4096).astype(np.float32)
+    assert not np.array_equal(c_oracle.warp_fold_gemv(b, z, 0), c_oracle.warp_fold_gemv(b, z, 1))

@@ -13,6 +13,16 @@ from oracle import synth
 pytestmark = pytest.mark.gpu
 
 
+def load_probe_module(L, c):
+    """The test/probe kernels live in their own cubin (tests/kernels/probe_kernels.cu), not in the library's image."""
+    from conftest import build_probe_kernels
+    image = build_probe_kernels().read_bytes()
+    buf = ctypes.create_string_buffer(image, len(image))
+    m = L.cl_b200_load_module(c, ctypes.cast(buf, ctypes.c_void_p), len(image))
+    assert m >= 0, L.cl_b200_last_error().decode()
+    return m
+
+
 @pytest.fixture()
 def ctx():
     L = lib()
@@ -34,7 +44,7 @@ def test_one_cta_bf16_gemm_matches_numpy(ctx, N, K):
     rng = np.random.default_rng(N + K)
     a32, a16 = bf16_round(rng.standard_normal((128, K)).astype(np.float32))
     b32, b16 = bf16_round(rng.standard_normal((N, K)).astype(np.float32))
-    m = L.cl_b200_builtin_module(c)
+    m = load_probe_module(L, c)
     bufs = [L.cl_cuda_create_buffer(c, a16.nbytes), L.cl_cuda_create_buffer(c, b16.nbytes),
             L.cl_cuda_create_buffer(c, 128 * N * 4), L.cl_cuda_create_buffer(c, 4)]
     assert min(bufs) >= 0
