@@ -393,6 +393,8 @@ def main():
                     help="with --batch > 1 on one GPU: do not also measure the batch-1 persistent kernel")
     ap.add_argument("--repeats", type=int, default=5,
                     help="how many times the K-step timed loop runs; the line reports the median repeat and the spread")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="profiling only: a model with this many layers (a small case for ncu); the line says so in config")
     ap.add_argument("--synthetic-kv", action="store_true",
                     help="batched workloads: start from a seeded synthetic KV cache at the prompt length instead of feeding the prompt")
     ap.add_argument("--workload", choices=("gptoss", "gptoss120b", "qwen2", "prefill"), default="gptoss",
@@ -433,6 +435,8 @@ def run_batch1(a, rank: int, world: int, local: int, ranks=None, emit: bool = Tr
     mx = a.step == "persistent" and a.experts == "block-scaled"
     cfg = dataclasses.replace(GPT_OSS_20B, max_seq=a.prompt + a.warmup + (max(1, a.repeats) + 1) * a.steps + 8,
                               flags=PDL | (PERSISTENT if a.step == "persistent" else 0) | (BLOCK_SCALED if mx else 0))
+    if a.layers:
+        cfg = dataclasses.replace(cfg, layers=a.layers)
     config = {"workload": "gpt-oss-20b decode, batch 1 per GPU, 2048-token prompt, greedy (BASELINE config 3)",
               "layers": cfg.layers, "hidden": cfg.hidden, "experts": cfg.experts, "top_k": cfg.top_k,
               "vocab": cfg.vocab, "context": a.prompt, "batch_per_gpu": 1,
@@ -591,6 +595,8 @@ def run_batched(a, rank: int, world: int, local: int):
         raise SystemExit(f"--batch {Bg} and the {model.experts} experts must be divisible by the {world} GPUs")
     per = Bg // world
     reps = max(1, a.repeats)
+    if a.layers:
+        model = dataclasses.replace(model, layers=a.layers)
     cfg = dataclasses.replace(model, batch=per, max_seq=a.prompt + a.warmup + (reps + 1) * a.steps + 8,
                               flags=PDL | BATCHED, ep_rank=rank, ep_world=world)
     metric = METRIC.replace("gpt-oss-20b", name)

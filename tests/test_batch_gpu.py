@@ -202,3 +202,11 @@ def test_batched_full_width_against_c_oracle():
     m.close()
     for o in oracles.values():
         o.close()
+
+
+def test_few_sequences_long_context_split_over_ctas():
+    # 2 sequences x 2 kv heads: the batched attention kernel gives every (sequence, kv head) several CTAs, each
+    # streaming a range of slices; their partial results are merged by the last one (5 slices at position 600)
+    c = small(batch=2, layers=2, max_seq=700, window=16, flags=PDL | BATCHED)
+    _, checked = drive_batched(c, 3, [7, 99], check_oracle=(0, 1), fill=True, start=600)
+    assert checked > 0
