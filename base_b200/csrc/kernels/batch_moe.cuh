@@ -11,15 +11,17 @@
 //   moe_expand_digits   f32 rows -> digits, in the order of the routing permutation (an expert's tokens contiguous):
 //                       dig [chunk of 8 K blocks][position][K block of the chunk][8 digit rows x 16 B] (the tokens of an
 //                       expert are ONE contiguous piece per chunk), em [position][96] block exponents
-//   moe_batch_mx_*      units = (expert, pass of <= 16 tokens, segment of <= 16 eight-row groups): N <= 128 rows per
-//                       instruction; producer warp (bulk copies: the segment's codes + scale words and the tokens'
-//                       digits of one chunk per ring slot), four scale warps (weights' scale words -> tensor memory),
-//                       issuer, four epilogue warps (each reads the accumulator rows of four tokens, adds the digit
-//                       rows, bias, clamped SwiGLU).
+//   mxfp4_retile_seg16  checkpoint layout -> per chunk of 8 K blocks and segment of 16 eight-row groups: the segment's codes
+//                       ([group][K block][8 rows x 16 B]) followed by its scale words laid out for tcgen05.cp
+//                       ([4-block group][32 lanes][16 B]: lane l = the words of rows l, 32 + l, 64 + l, 96 + l)
+//   moe_batch_mx_*      units = (expert, pass of <= 16 tokens, segment): N <= 128 rows per instruction; producer warp
+//                       (two bulk copies per ring slot: the segment's piece and the tokens' digits of one chunk), issuer
+//                       (per 4 K blocks: one tcgen05.cp of the weights' scale words, two instructions), four epilogue
+//                       warps (each reads the accumulator rows of four tokens, adds the digit rows, bias, clamped SwiGLU).
 // Scale factors in tensor memory: the tensor core's lane quarter q (accumulator rows 32 q ..) takes BOTH operands' scales
-// from its own 32 lanes, so every quarter needs a copy (what tcgen05.cp ... warpx4 does by itself); here the copies are
-// written with tcgen05.st by one warp per quarter.  With one token only quarter 0 carries results, which is why the
-// one-token kernels write a single copy.
+// from its own 32 lanes, so every quarter needs a copy.  tcgen05.cp ... 32x128b.warpx4 writes all four by itself (the
+// weights' scales); the tokens' scales are computed here and written with tcgen05.st by one warp per quarter.  With one
+// token only quarter 0 carries results, which is why the one-token kernels write a single copy.
 // Routing tables are those of moe_route_tables_many (count / offset / perm).  Every wait is bounded.
 #pragma once
 #include "moe_mx.cuh"
@@ -31,7 +33,7 @@ constexpr int kBmSlots = 5;
 constexpr int kBmBBytes = kBmGroups * (kBmKc * 128 + 64);      // 17408: codes + scale words of a chunk
 constexpr int kBmABytes = kBmKc * kBmTok * 128;                // 16384: digits of a chunk
 constexpr int kBmSlotBytes = kBmBBytes + kBmABytes;
-constexpr int kBmThreads = 320;              // warps 0..3 epilogue, 4..7 weights' scale words, 8 issuer, 9 producer
+constexpr int kBmThreads = 192;              // warps 0..3 epilogue, 4 issuer, 5 producer
 constexpr int kBmEmStride = 96;
 constexpr int kBmMaxUnits = 192;             // units one CTA can take
 
@@ -98,6 +100,66 @@ moe_expand_digits(const float *__restrict__ x, const int *__restrict__ route, ui
   }
 }
 
+// ---- weights: checkpoint layout -> segments of 16 groups ---------------------------------------------------
+B200_DEVICE size_t seg16_bytes(int kcc, int ng) { return size_t(ng) * kcc * 128 + size_t((kcc + 3) / 4) * 512; }
+B200_DEVICE size_t seg16_chunk_bytes(int kcc, int G) {
+  const int nseg = (G + kBmGroups - 1) / kBmGroups;
+  return size_t(G) * kcc * 128 + size_t(nseg) * ((kcc + 3) / 4) * 512;
+}
+B200_DEVICE size_t seg16_matrix_bytes(int kblocks, int G) {
+  const int full = kblocks / kBmKc, tail = kblocks - full * kBmKc;
+  return size_t(full) * seg16_chunk_bytes(kBmKc, G) + (tail ? seg16_chunk_bytes(tail, G) : 0);
+}
+// start of segment `seg` of chunk c (every earlier chunk and segment is a full one)
+B200_DEVICE size_t seg16_offset(int c, int seg, int kcc, int G) {
+  return size_t(c) * seg16_chunk_bytes(kBmKc, G) + size_t(seg) * seg16_bytes(kcc, kBmGroups);
+}
+
+struct RetileSegArgs { int R, K, n_mat; };
+
+// codes [n_mat][R][K / 2], scales [n_mat][R][K / 32]; one thread per 16 bytes of codes, and per scale word.
+extern "C" __global__ void __launch_bounds__(256)
+mxfp4_retile_seg16(const uint8_t *__restrict__ codes, const uint8_t *__restrict__ scales, uint8_t *__restrict__ out, RetileSegArgs a) {
+  const int kblocks = a.K >> 5, G = a.R >> 3, nch = (kblocks + kBmKc - 1) / kBmKc, nseg = (G + kBmGroups - 1) / kBmGroups;
+  const size_t mbytes = seg16_matrix_bytes(kblocks, G);
+  const size_t gid = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  const size_t total = size_t(a.n_mat) * a.R * kblocks;
+  if (gid < total) {
+    const int kb = int(gid % kblocks);
+    const size_t row_all = gid / kblocks;
+    const int row = int(row_all % a.R);
+    const size_t mat = row_all / a.R;
+    const int c = kb / kBmKc, kbl = kb % kBmKc, kcc = min(kBmKc, kblocks - c * kBmKc), g = row >> 3, seg = g / kBmGroups;
+    uint8_t *dst = out + mat * mbytes + seg16_offset(c, seg, kcc, G) + (size_t(g % kBmGroups) * kcc + kbl) * 128 + (row & 7) * 16;
+    *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(codes + row_all * (a.K >> 1) + size_t(kb) * 16);
+  }
+  // scale words: (matrix, chunk, segment, 4-block group j, lane l, row group q)
+  const size_t stotal = size_t(a.n_mat) * nch * nseg * 2 * 128;
+  if (gid < stotal) {
+    const int q = int(gid & 3), l = int((gid >> 2) & 31), j = int((gid >> 7) & 1);
+    size_t rest = gid >> 8;
+    const int seg = int(rest % nseg);
+    rest /= nseg;
+    const int c = int(rest % nch);
+    const size_t mat = rest / nch;
+    const int kcc = min(kBmKc, kblocks - c * kBmKc), ng = min(kBmGroups, G - seg * kBmGroups);
+    if (j < (kcc + 3) / 4) {
+      const int g = 4 * q + (l >> 3);                       // group of row 32 q + l within the segment
+      uint32_t w = 0x7f7f7f7fu;
+      if (g < ng) {
+        w = 0;
+        const size_t row = mat * a.R + size_t(seg * kBmGroups + g) * 8 + (l & 7);
+        for (int b = 0; b < 4; ++b) {
+          const int kb = c * kBmKc + 4 * j + b;
+          w |= (kb < kblocks ? uint32_t(scales[row * kblocks + kb]) : 127u) << (8 * b);
+        }
+      }
+      uint8_t *dst = out + mat * mbytes + seg16_offset(c, seg, kcc, G) + size_t(ng) * kcc * 128 + j * 512 + l * 16 + q * 4;
+      *reinterpret_cast<uint32_t *>(dst) = w;
+    }
+  }
+}
+
 // ---- the expert kernel -----------------------------------------------------------------------------------
 struct BatchMxArgs {
   MoeDims d;
@@ -108,7 +170,7 @@ struct BatchMxArgs {
 struct BmUnit { int16_t e, pass, g0, ng; };
 
 struct BmBars {
-  uint64_t full[kBmSlots], empty[kBmSlots], sready[kBmSlots], done[2], uready[2];
+  uint64_t full[kBmSlots], empty[kBmSlots], done[2], uready[2];
   uint32_t tmem_base;
   int abort, n_units, u_base;
 };
@@ -126,18 +188,21 @@ B200_DEVICE int bm_smem_bytes() { return kBmSlots * kBmSlotBytes + kBmMaxUnits *
 
 // Two instructions over four consecutive K blocks (scale bytes 0,1 then 2,3 of one column group), issued by an
 // elected lane of the converged warp; the second one's operands are a_step / b_step descriptor units further.
+// Before them the same lane copies the weights' scale words of these four K blocks from shared memory (32 lanes x 16 B)
+// into the four columns at sfb_tmem of every lane quarter; copies and instructions of one thread execute in order.
 B200_DEVICE void bm_mma_pair_warp(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc01, uint32_t idesc23,
                                   uint32_t sfa_tmem, uint32_t sfb_tmem, bool accumulate_first, bool second, uint32_t a_step,
-                                  uint32_t b_step) {
+                                  uint32_t b_step, uint64_t sf_desc) {
   asm volatile(
       "{\n.reg .pred p, q, e, e2;\n.reg .b64 a2, b2, sa, sb;\n"
       "elect.sync _|e, 0xffffffff;\n"
+      "@e tcgen05.cp.cta_group::1.32x128b.warpx4 [%7], %11;\n"
       "setp.ne.b32 p, %5, 0;\nsetp.eq.b32 q, %5, %5;\nsetp.ne.b32 e2, %8, 0;\nand.pred e2, e2, e;\n"
       "@e tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%6], [%7], p;\n"
       "cvt.u64.u32 sa, %9;\ncvt.u64.u32 sb, %10;\nadd.u64 a2, %1, sa;\nadd.u64 b2, %2, sb;\n"
       "@e2 tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], a2, b2, %4, [%6], [%7], q;\n}\n" ::"r"(d_tmem),
       "l"(adesc), "l"(bdesc), "r"(idesc01), "r"(idesc23), "r"(uint32_t(accumulate_first)), "r"(sfa_tmem), "r"(sfb_tmem),
-      "r"(uint32_t(second)), "r"(a_step), "r"(b_step)
+      "r"(uint32_t(second)), "r"(a_step), "r"(b_step), "l"(sf_desc)
       : "memory");
 }
 
@@ -163,7 +228,6 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
   if (tid == 0) {
     for (int i = 0; i < kBmSlots; ++i) { mbar_init(&bars->full[i], 1); mbar_init(&bars->empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&bars->done[i], 1); mbar_init(&bars->uready[i], 4); }
-    for (int i = 0; i < kBmSlots; ++i) mbar_init(&bars->sready[i], 4);
     bars->abort = 0;
   }
   fence_barrier_init();
@@ -202,9 +266,9 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
     units[i] = u;
   }
   __syncthreads();
-  const size_t mbytes = mxw_matrix_bytes(kblocks, kBmKc, R);
+  const size_t mbytes = seg16_matrix_bytes(kblocks, G);
 
-  if (warp == 9) {
+  if (warp == 5) {
     // ---- producer
     if (lane == 0) {
       uint32_t q = 0;
@@ -215,43 +279,16 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
         for (int c = 0; c < nch; ++c, ++q) {
           const uint32_t s = q % kBmSlots;
           if (q >= kBmSlots && !bm_wait(&bars->empty[s], ((q / kBmSlots) - 1) & 1, bars, status, 72)) { ui = n_units; break; }
-          const int kcc = min(kBmKc, kblocks - c * kBmKc), gb = mxw_group_bytes(kcc);
+          const int kcc = min(kBmKc, kblocks - c * kBmKc);
+          const uint32_t bbytes = uint32_t(seg16_bytes(kcc, u.ng));
           uint8_t *dst = ring + size_t(s) * kBmSlotBytes;
-          mbar_expect_tx(&bars->full[s], uint32_t(u.ng * gb + nt * kBmKc * 128));
-          bulk_g2s(dst, wexp + mxw_chunk_base(c, kBmKc, R) + size_t(u.g0) * gb, uint32_t(u.ng * gb), &bars->full[s]);
+          mbar_expect_tx(&bars->full[s], bbytes + uint32_t(nt * kBmKc * 128));
+          bulk_g2s(dst, wexp + seg16_offset(c, u.g0 / kBmGroups, kcc, G), bbytes, &bars->full[s]);
           bulk_g2s(dst + kBmBBytes, dig + (size_t(c) * a.P + off) * (kBmKc * 128), uint32_t(nt * kBmKc * 128), &bars->full[s]);
         }
       }
     }
-  } else if (warp >= 4 && warp < 8) {
-    // ---- weights' scale words -> tensor memory, per ring slot: warp 4 + q writes lane quarter q's copy
-    const uint32_t tq = uint32_t((warp & 3) * 32) << 16;
-    uint32_t q = 0;
-    for (int ui = 0; ui < n_units; ++ui) {
-      const BmUnit u = units[ui];
-      const int N = u.ng * 8;
-      bool ok = true;
-      for (int c = 0; c < nch && ok; ++c, ++q) {
-        const uint32_t s = q % kBmSlots;
-        ok = bm_wait(&bars->full[s], (q / kBmSlots) & 1, bars, status, 73);
-        if (!ok) break;
-        const int kcc = min(kBmKc, kblocks - c * kBmKc), gb = mxw_group_bytes(kcc);
-        const uint8_t *sw = ring + size_t(s) * kBmSlotBytes + size_t(lane >> 3) * gb + kcc * 128 + (lane & 7) * 4;
-        for (int j = 0; j < (kcc + 3) / 4; ++j) {
-          uint32_t w[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-            w[i] = lane + 32 * i < N ? *reinterpret_cast<const uint32_t *>(sw + size_t(4 * i) * gb + j * 32) : 0u;
-          tc_st_cols4(tSFB + tq + s * 8 + j * 4, w[0], w[1], w[2], w[3]);
-        }
-        tc_wait_st();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->sready[s]);
-      }
-      if (!ok) break;
-    }
-  } else if (warp == 8) {
+  } else if (warp == 4) {
     // ---- issuer (whole warp, an elected lane issues)
     uint32_t q = 0;
     for (int ui = 0; ui < n_units; ++ui) {
@@ -264,17 +301,18 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
       bool ok = true;
       for (int c = 0; c < nch && ok; ++c, ++q) {
         const uint32_t s = q % kBmSlots;
-        ok = bm_wait(&bars->sready[s], (q / kBmSlots) & 1, bars, status, 75);
+        ok = bm_wait(&bars->full[s], (q / kBmSlots) & 1, bars, status, 75);
         if (!ok) break;
         tc_fence_after_sync();
-        const int kcc = min(kBmKc, kblocks - c * kBmKc), gb = mxw_group_bytes(kcc);
-        const uint32_t sb = smem_u32(ring + size_t(s) * kBmSlotBytes), sa = sb + kBmBBytes;
+        const int kcc = min(kBmKc, kblocks - c * kBmKc);
+        const uint32_t sb = smem_u32(ring + size_t(s) * kBmSlotBytes), sa = sb + kBmBBytes, ssf = sb + uint32_t(u.ng * kcc * 128);
         for (int pp = 0; 4 * pp < kcc; ++pp) {
           // A in the slot: [token][K block of the chunk][8 digit rows x 16 B]: K blocks 128 B apart, tokens 1 KB apart
+          // B in the slot: [group][K block][8 rows x 16 B]: K blocks 128 B apart, groups kcc x 128 B apart
           const uint64_t da = tc_smem_desc(sa + uint32_t(4 * pp) * 128, 128, kBmKc * 128);
-          const uint64_t db = tc_smem_desc(sb + uint32_t(4 * pp) * 128, 128, uint32_t(gb));
+          const uint64_t db = tc_smem_desc(sb + uint32_t(4 * pp) * 128, 128, uint32_t(kcc * 128));
           bm_mma_pair_warp(tDu, da, db, id0, id2, tSFAu + 4 * uint32_t(c * (kBmKc >> 2) + pp), tSFB + s * 8 + uint32_t(pp) * 4,
-                           !(c == 0 && pp == 0), 4 * pp + 2 < kcc, 256u >> 4, 256u >> 4);
+                           !(c == 0 && pp == 0), 4 * pp + 2 < kcc, 256u >> 4, 256u >> 4, tc_smem_desc(ssf + uint32_t(pp) * 512, 16, 128));
         }
         tc_commit_warp(&bars->empty[s], true);
         tc_commit_warp(&bars->done[ui & 1], c == nch - 1);
