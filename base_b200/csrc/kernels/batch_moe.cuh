@@ -29,10 +29,13 @@
 constexpr int kBmTok = 16;                   // tokens per pass
 constexpr int kBmGroups = 16;                // 8-row groups per unit (N = 128)
 constexpr int kBmKc = 8;                     // K blocks per chunk
-constexpr int kBmSlots = 5;
+constexpr int kBmSlots = 8;                  // at most; the ring holds as many slots as fit
 constexpr int kBmBBytes = kBmGroups * (kBmKc * 128 + 64);      // 17408: codes + scale words of a chunk
-constexpr int kBmABytes = kBmKc * kBmTok * 128;                // 16384: digits of a chunk
-constexpr int kBmSlotBytes = kBmBBytes + kBmABytes;
+constexpr int kBmRingBytes = 8 * (kBmBBytes + 8 * kBmKc * 128);  // 204800: eight slots when no pass has more than 8 tokens
+// A ring slot = [digits of the unit's tokens for one chunk: 1 KB per token, sized for the most tokens any of this CTA's
+// units has][the segment's piece, kBmBBytes reserved].  The tensor core reads 128 A rows = 16 KB from the digits' base
+// whatever the token count: what lies beyond the tokens is this slot's own weight piece (results of those rows are
+// never read).  Fewer tokens per pass = smaller slots = more weight bytes in flight.
 constexpr int kBmThreads = 192;              // warps 0..3 epilogue, 4 issuer, 5 producer
 constexpr int kBmEmStride = 96;
 constexpr int kBmMaxUnits = 192;             // units one CTA can take
@@ -172,7 +175,7 @@ struct BmUnit { int16_t e, pass, g0, ng; };
 struct BmBars {
   uint64_t full[kBmSlots], empty[kBmSlots], done[2], uready[2];
   uint32_t tmem_base;
-  int abort, n_units, u_base;
+  int abort, n_units, u_base, max_nt;
 };
 
 B200_DEVICE bool bm_wait(uint64_t *bar, uint32_t parity, BmBars *b, int *status, int code) {
@@ -184,7 +187,7 @@ B200_DEVICE bool bm_wait(uint64_t *bar, uint32_t parity, BmBars *b, int *status,
   return false;
 }
 
-B200_DEVICE int bm_smem_bytes() { return kBmSlots * kBmSlotBytes + kBmMaxUnits * int(sizeof(BmUnit)) + int(sizeof(BmBars)) + 64; }
+B200_DEVICE int bm_smem_bytes() { return kBmRingBytes + kBmMaxUnits * int(sizeof(BmUnit)) + int(sizeof(BmBars)) + 64; }
 
 // Two instructions over four consecutive K blocks (scale bytes 0,1 then 2,3 of one column group), issued by an
 // elected lane of the converged warp; the second one's operands are a_step / b_step descriptor units further.
@@ -221,8 +224,8 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
   const int kblocks = K >> 5, nch = (kblocks + kBmKc - 1) / kBmKc, G = R >> 3, nseg = (G + kBmGroups - 1) / kBmGroups;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   uint8_t *ring = dyn_smem;
-  BmUnit *units = reinterpret_cast<BmUnit *>(dyn_smem + kBmSlots * kBmSlotBytes);
-  BmBars *bars = reinterpret_cast<BmBars *>(dyn_smem + kBmSlots * kBmSlotBytes + kBmMaxUnits * sizeof(BmUnit));
+  BmUnit *units = reinterpret_cast<BmUnit *>(dyn_smem + kBmRingBytes);
+  BmBars *bars = reinterpret_cast<BmBars *>(dyn_smem + kBmRingBytes + kBmMaxUnits * sizeof(BmUnit));
   const int *count = route + 1, *offset = route + 1 + E, *perm = route + 1 + E + (E + 1) + E;
 
   if (tid == 0) {
@@ -248,6 +251,7 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
     const int u0 = int((long long)total * blockIdx.x / gridDim.x), u1 = int((long long)total * (blockIdx.x + 1) / gridDim.x);
     bars->u_base = u0;
     bars->n_units = u1 - u0;
+    bars->max_nt = 0;
     if (u1 - u0 > kBmMaxUnits) { bars->n_units = 0; atomicCAS(status, 0, 71); }
   }
   __syncthreads();
@@ -264,9 +268,12 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
     BmUnit u;
     u.e = int16_t(e); u.pass = int16_t(pass); u.g0 = int16_t(seg * kBmGroups); u.ng = int16_t(min(kBmGroups, G - seg * kBmGroups));
     units[i] = u;
+    atomicMax(&bars->max_nt, min(kBmTok, count[min(e, a.lo + a.n - 1)] - pass * kBmTok));
   }
   __syncthreads();
   const size_t mbytes = seg16_matrix_bytes(kblocks, G);
+  const uint32_t a_bytes = uint32_t(max(bars->max_nt, 1)) * (kBmKc * 128), slot_bytes = a_bytes + kBmBBytes;
+  const uint32_t n_slots = min(uint32_t(kBmSlots), uint32_t(kBmRingBytes) / slot_bytes);
 
   if (warp == 5) {
     // ---- producer
@@ -277,14 +284,14 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
         const int off = offset[u.e] + u.pass * kBmTok, nt = min(kBmTok, count[u.e] - u.pass * kBmTok);
         const uint8_t *wexp = W + size_t(u.e - a.lo) * mbytes;
         for (int c = 0; c < nch; ++c, ++q) {
-          const uint32_t s = q % kBmSlots;
-          if (q >= kBmSlots && !bm_wait(&bars->empty[s], ((q / kBmSlots) - 1) & 1, bars, status, 72)) { ui = n_units; break; }
+          const uint32_t s = q % n_slots;
+          if (q >= n_slots && !bm_wait(&bars->empty[s], ((q / n_slots) - 1) & 1, bars, status, 72)) { ui = n_units; break; }
           const int kcc = min(kBmKc, kblocks - c * kBmKc);
           const uint32_t bbytes = uint32_t(seg16_bytes(kcc, u.ng));
-          uint8_t *dst = ring + size_t(s) * kBmSlotBytes;
+          uint8_t *dst = ring + size_t(s) * slot_bytes;
           mbar_expect_tx(&bars->full[s], bbytes + uint32_t(nt * kBmKc * 128));
-          bulk_g2s(dst, wexp + seg16_offset(c, u.g0 / kBmGroups, kcc, G), bbytes, &bars->full[s]);
-          bulk_g2s(dst + kBmBBytes, dig + (size_t(c) * a.P + off) * (kBmKc * 128), uint32_t(nt * kBmKc * 128), &bars->full[s]);
+          bulk_g2s(dst + a_bytes, wexp + seg16_offset(c, u.g0 / kBmGroups, kcc, G), bbytes, &bars->full[s]);
+          bulk_g2s(dst, dig + (size_t(c) * a.P + off) * (kBmKc * 128), uint32_t(nt * kBmKc * 128), &bars->full[s]);
         }
       }
     }
@@ -300,12 +307,12 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
       const uint32_t id0 = mx_idesc(128, N, 0, 0), id2 = mx_idesc(128, N, 2, 2);
       bool ok = true;
       for (int c = 0; c < nch && ok; ++c, ++q) {
-        const uint32_t s = q % kBmSlots;
-        ok = bm_wait(&bars->full[s], (q / kBmSlots) & 1, bars, status, 75);
+        const uint32_t s = q % n_slots;
+        ok = bm_wait(&bars->full[s], (q / n_slots) & 1, bars, status, 75);
         if (!ok) break;
         tc_fence_after_sync();
         const int kcc = min(kBmKc, kblocks - c * kBmKc);
-        const uint32_t sb = smem_u32(ring + size_t(s) * kBmSlotBytes), sa = sb + kBmBBytes, ssf = sb + uint32_t(u.ng * kcc * 128);
+        const uint32_t sa = smem_u32(ring + size_t(s) * slot_bytes), sb = sa + a_bytes, ssf = sb + uint32_t(u.ng * kcc * 128);
         for (int pp = 0; 4 * pp < kcc; ++pp) {
           // A in the slot: [token][K block of the chunk][8 digit rows x 16 B]: K blocks 128 B apart, tokens 1 KB apart
           // B in the slot: [group][K block][8 rows x 16 B]: K blocks 128 B apart, groups kcc x 128 B apart
