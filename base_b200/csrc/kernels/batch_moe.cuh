@@ -176,6 +176,7 @@ struct BmBars {
   uint64_t full[kBmSlots], empty[kBmSlots], done[2], uready[2];
   uint32_t tmem_base;
   int abort, n_units, u_base, max_nt;
+  uint32_t em_s[2][kBmTok * (kBmEmStride / 4)];      // block exponents of the tokens of two units in flight
 };
 
 B200_DEVICE bool bm_wait(uint64_t *bar, uint32_t parity, BmBars *b, int *status, int code) {
@@ -335,13 +336,17 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
       // row 32 q + lane of A = digit row (lane & 7) of token 4 q + (lane >> 3); scale byte = exponent - 21 + 3 (7 - digit row)
       const uint32_t adj = 0x01010101u * uint32_t(3 * (7 - (lane & 7)));
       const uint32_t base = tSFA + uint32_t(ui & 1) * 96u + (uint32_t(warp * 32) << 16);
+      // the tokens' exponent rows are one contiguous piece: all loads in flight at once, then shared memory
+      uint32_t *es = bars->em_s[ui & 1];
+      const uint32_t *src = reinterpret_cast<const uint32_t *>(em + size_t(off) * kBmEmStride);
+      for (int i = tid; i < nt * (kBmEmStride / 4); i += 128) es[i] = __ldcg(src + i);
+      asm volatile("bar.sync 2, 128;" ::: "memory");
       for (int gg = 0; gg < (kblocks + 3) / 4; ++gg) {
         uint32_t w[4];
 #pragma unroll
         for (int qd = 0; qd < 4; ++qd) {
           const int t = 4 * qd + (lane >> 3);
-          w[qd] = t < nt ? __ldcg(reinterpret_cast<const uint32_t *>(em + size_t(off + t) * kBmEmStride) + gg) + adj - 0x15151515u
-                         : 0x7f7f7f7fu;
+          w[qd] = t < nt ? es[t * (kBmEmStride / 4) + gg] + adj - 0x15151515u : 0x7f7f7f7fu;
         }
         tc_st_cols4(base + 4 * gg, w[0], w[1], w[2], w[3]);
       }

@@ -95,7 +95,7 @@ struct TablesManyArgs { int A, E, lo, n; };
 struct CombineRangeArgs { int H, top_k, lo, n; };
 struct RetileSegArgs { int R, K, n_mat; };
 constexpr int kBdThreads = 192, kBdSmemBytes = 6 * (8192 + 16 * 1024) + 64 * 129 * 4 + 512;
-constexpr int kBmThreads = 192, kBmSmemBytes = 8 * (16 * (8 * 128 + 64) + 8 * 8 * 128) + 192 * 8 + 256;
+constexpr int kBmThreads = 192, kBmSmemBytes = 8 * (16 * (8 * 128 + 64) + 8 * 8 * 128) + 192 * 8 + 4096;
 struct SynthArgs { unsigned long long n; uint32_t tensor, seed; int kind; float c; int lo, span; unsigned long long first; };
 
 // Tensor kinds (tensor id = layer * 32 + kind; globals use layer = 1000).
