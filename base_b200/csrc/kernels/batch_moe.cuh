@@ -364,11 +364,22 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
       // accumulator was read in the last iteration), so the issuer never waits for this warp
       if (ui + 1 < n_units) stage_scales(ui + 1);
       const uint32_t tDu = tD + uint32_t(ui & 1) * 128u;
-      if (!bm_wait(&bars->done[ui & 1], (ui >> 1) & 1, bars, status, 76)) break;
-      tc_fence_after_sync();
       const int tt = 4 * warp + (lane >> 3);
       const int asg = tt < nt ? perm[off + tt] : 0;
-      for (int c0 = 0; c0 < N; c0 += 32) {
+      // this lane's biases travel while the weights stream
+      float4 bpre[kBmGroups * 8 / 32];
+#pragma unroll
+      for (int i = 0; i < kBmGroups * 8 / 32; ++i) {
+        const int col = 32 * i + 4 * (lane & 7);
+        bpre[i] = (tt < nt && col < N) ? __ldg(reinterpret_cast<const float4 *>(bias + size_t(u.e) * R + u.g0 * 8 + col))
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      if (!bm_wait(&bars->done[ui & 1], (ui >> 1) & 1, bars, status, 76)) break;
+      tc_fence_after_sync();
+#pragma unroll
+      for (int ci = 0; ci < kBmGroups * 8 / 32; ++ci) {
+        const int c0 = 32 * ci;
+        if (c0 >= N) break;
         float v[32];
         {
           float lo16[16], hi16[16];
@@ -396,7 +407,7 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
         const int col = c0 + 4 * (lane & 7);
         if (tt < nt && col < N) {
           const int row = u.g0 * 8 + col;
-          const float4 b = __ldg(reinterpret_cast<const float4 *>(bias + size_t(u.e) * R + row));
+          const float4 b = bpre[ci];
           if (GATE_UP) {
             *reinterpret_cast<float2 *>(out + size_t(asg) * (R >> 1) + (row >> 1)) =
                 make_float2(swiglu_clamped(r4[0] + b.x, r4[1] + b.y, d.alpha, d.limit),
