@@ -36,8 +36,36 @@ B200_DEVICE void ab_prefetch(AttnBatchSmem &sm, int stage, int j0, int nj, size_
   asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
+// ---- tensor-core pieces (mma.sync m16n8k16, bf16 inputs, f32 accumulate) --------------------------------------
+// A rows 0..7 = the group's q heads (or their probabilities) rounded to bf16, rows 8..15 = what the rounding left
+// (x - bf16(x)), so that hi + lo carries the f32 value to 2^-17; the two halves of an accumulator column are added
+// afterwards.  K and V are bf16 in the cache, so the products are exact.
+B200_DEVICE uint32_t ab_pack_hi(float a, float b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t *>(&h);
+}
+B200_DEVICE uint32_t ab_pack_lo(float a, float b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  const float2 f = __bfloat1622float2(h);
+  const __nv_bfloat162 l = __floats2bfloat162_rn(a - f.x, b - f.y);
+  return *reinterpret_cast<const uint32_t *>(&l);
+}
+B200_DEVICE void ab_mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+B200_DEVICE void ab_ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
 // grid = (S, NKV, B), 256 threads, dynamic shared memory sizeof(AttnBatchSmem).
 // part_o [B][NQ][max_splits][64], part_ml [B][NQ][max_splits][2], counters [B][NKV] (zero on entry, zero on exit).
+// Warp w owns positions [16 w, 16 w + 16) of every slice, for all q heads of the group: Q K^T is two n-tiles x four
+// k-steps, P V one k-step x eight n-tiles; its running maximum, denominator and output stay in registers over the
+// slices and the eight warps are merged once at the end, in warp order.
 extern "C" __global__ void __launch_bounds__(kAbThreads, 2)
 attn_decode_batch(const float *__restrict__ qkv, const float *__restrict__ rope, const int *__restrict__ meta,
                   uint16_t *kcache, uint16_t *vcache, const float *__restrict__ sinks, float *__restrict__ part_o,
@@ -45,6 +73,7 @@ attn_decode_batch(const float *__restrict__ qkv, const float *__restrict__ rope,
   AttnBatchSmem &sm = *reinterpret_cast<AttnBatchSmem *>(dyn_smem);
   constexpr int HD = 64, HALF = 32;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, c = lane & 3;
   const int sx = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int G = a.NQ / a.NKV, QD = a.NQ * HD;
   const int pos = meta[2 * b + 1];          // written before this step's graph is launched (or by the last step's argmax)
@@ -76,7 +105,23 @@ attn_decode_batch(const float *__restrict__ qkv, const float *__restrict__ rope,
     sm.q[gq][d] = rlo;
     sm.q[gq][d + HALF] = rhi;
   }
-  float M = -INFINITY, L = 0.f, o0 = 0.f, o1 = 0.f;      // warp = q head, lane = two dimensions
+  __syncthreads();
+  // ---- this thread's q fragments: head g, dims 16 ks + 2 c (+1) and + 8
+  uint32_t qa[4][4];
+#pragma unroll
+  for (int ks = 0; ks < 4; ++ks) {
+    const float2 x0 = *reinterpret_cast<const float2 *>(&sm.q[g][16 * ks + 2 * c]);
+    const float2 x1 = *reinterpret_cast<const float2 *>(&sm.q[g][16 * ks + 8 + 2 * c]);
+    qa[ks][0] = ab_pack_hi(x0.x, x0.y);
+    qa[ks][1] = ab_pack_lo(x0.x, x0.y);
+    qa[ks][2] = ab_pack_hi(x1.x, x1.y);
+    qa[ks][3] = ab_pack_lo(x1.x, x1.y);
+  }
+  float M = -INFINITY, L = 0.f;              // head g, this warp's positions; L is this thread's share
+  float o[8][4];                             // n-tile (8 dims) x {row g: cols 2c, 2c+1; row g + 8: the same}
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const int p0 = 16 * warp;
 #pragma unroll 1
   for (int sl = s_lo; sl < s_hi; ++sl) {
     const int st = (sl - s_lo) & 1;
@@ -88,9 +133,9 @@ attn_decode_batch(const float *__restrict__ qkv, const float *__restrict__ rope,
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
-    __syncthreads();                                   // this slice's rows have landed for every thread; q is staged
+    __syncthreads();                                   // this slice's rows have landed for every thread
     if (sl == nsplit - 1) {
-      // the slice that ends at `pos` appends the new row (cache and shared memory)
+      // the slice that ends at `pos` appends the new row (cache and shared memory) and clears the V rows past it
       const size_t slot = (head_base + size_t(pos % a.cache_len)) * HD;
       const int row = pos - j0;
       if (tid < HALF) {
@@ -108,75 +153,91 @@ attn_decode_batch(const float *__restrict__ qkv, const float *__restrict__ rope,
         vcache[slot + d] = bv;
         sm.v[st][row][d] = bv;
       }
+      for (int i = tid; i < (kAttnSplit - nj) * 8; i += kAbThreads)      // a zero probability times stale bits must stay zero
+        *reinterpret_cast<uint4 *>(&sm.v[st][nj + (i >> 3)][(i & 7) * 8]) = make_uint4(0, 0, 0, 0);
       __syncthreads();
     }
-    // ---- scores: thread = (position, half of the q heads)
-    {
-      const int p = tid >> 1, h0 = (tid & 1) * 4;
-      if (p < nj) {
-        float s[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 2
-        for (int ch = 0; ch < 8; ++ch) {
-          const uint4 kw = *reinterpret_cast<const uint4 *>(&sm.k[st][p][ch * 8]);
-          const float kf[8] = {bf16_lo(kw.x), bf16_hi(kw.x), bf16_lo(kw.y), bf16_hi(kw.y),
-                               bf16_lo(kw.z), bf16_hi(kw.z), bf16_lo(kw.w), bf16_hi(kw.w)};
+    if (p0 < nj) {
+      // ---- scores of positions p0 + {0..7} (tile 0) and p0 + {8..15} (tile 1) for head g
+      float sc[2][4];
 #pragma unroll
-          for (int h = 0; h < 4; ++h) {
-            const float4 q0 = *reinterpret_cast<const float4 *>(&sm.q[h0 + h][ch * 8]);
-            const float4 q1 = *reinterpret_cast<const float4 *>(&sm.q[h0 + h][ch * 8 + 4]);
-            float t = s[h];
-            t = fmaf(q0.x, kf[0], t); t = fmaf(q0.y, kf[1], t); t = fmaf(q0.z, kf[2], t); t = fmaf(q0.w, kf[3], t);
-            t = fmaf(q1.x, kf[4], t); t = fmaf(q1.y, kf[5], t); t = fmaf(q1.z, kf[6], t); t = fmaf(q1.w, kf[7], t);
-            s[h] = t;
-          }
+      for (int t = 0; t < 2; ++t) {
+        sc[t][0] = sc[t][1] = sc[t][2] = sc[t][3] = 0.f;
+        const uint16_t *krow = &sm.k[st][p0 + 8 * t + g][0];
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint32_t b0 = *reinterpret_cast<const uint32_t *>(krow + 16 * ks + 2 * c);
+          const uint32_t b1 = *reinterpret_cast<const uint32_t *>(krow + 16 * ks + 8 + 2 * c);
+          ab_mma(sc[t], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
         }
-#pragma unroll
-        for (int h = 0; h < 4; ++h) sm.s[h0 + h][p] = s[h];
       }
-    }
-    __syncthreads();
-    // ---- running softmax and P V: warp = q head
-    {
-      float v[kAttnSplit / 32], m = -INFINITY;
+      // this thread: head g, positions p0 + 8 t + 2 c (+1); the lo rows (g + 8) are added to the hi rows
+      float s4[4];
+      float m = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < kAttnSplit / 32; ++i) {
-        const int p = lane + 32 * i;
-        v[i] = p < nj ? sm.s[warp][p] : -INFINITY;
-        m = fmaxf(m, v[i]);
-      }
-      m = warp_max(m);
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int p = p0 + 8 * t + 2 * c + e;
+          s4[2 * t + e] = p < nj ? sc[t][e] + sc[t][2 + e] : -INFINITY;
+          m = fmaxf(m, s4[2 * t + e]);
+        }
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+      m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
       const float Mn = fmaxf(M, m);
       const float f = (M == -INFINITY) ? 0.f : __expf(M - Mn);
-      float l = 0.f;
+      float pr[4];
 #pragma unroll
-      for (int i = 0; i < kAttnSplit / 32; ++i) {
-        const int p = lane + 32 * i;
-        const float e = p < nj ? __expf(v[i] - Mn) : 0.f;
-        sm.s[warp][p] = e;
-        l += e;
-      }
-      l = warp_sum(l);
-      L = fmaf(L, f, l);
+      for (int i = 0; i < 4; ++i) pr[i] = s4[i] == -INFINITY ? 0.f : __expf(s4[i] - Mn);
+      L = fmaf(L, f, (pr[0] + pr[1]) + (pr[2] + pr[3]));
       M = Mn;
-      __syncwarp();
-      float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
-#pragma unroll 4
-      for (int p = 0; p + 1 < nj; p += 2) {
-        const float pa = sm.s[warp][p], pb = sm.s[warp][p + 1];
-        const uint32_t va = *reinterpret_cast<const uint32_t *>(&sm.v[st][p][2 * lane]);
-        const uint32_t vb = *reinterpret_cast<const uint32_t *>(&sm.v[st][p + 1][2 * lane]);
-        a0 = fmaf(pa, bf16_lo(va), a0); a1 = fmaf(pa, bf16_hi(va), a1);
-        b0 = fmaf(pb, bf16_lo(vb), b0); b1 = fmaf(pb, bf16_hi(vb), b1);
+      // probabilities as the A operand: k = position within the 16: tile 0 -> k 2c, 2c+1; tile 1 -> k 8 + 2c, ...
+      const uint32_t pa0 = ab_pack_hi(pr[0], pr[1]), pa1 = ab_pack_lo(pr[0], pr[1]);
+      const uint32_t pa2 = ab_pack_hi(pr[2], pr[3]), pa3 = ab_pack_lo(pr[2], pr[3]);
+      // V of these 16 positions, transposed by ldmatrix: lane l addresses row p0 + 8 ((l >> 3) & 1) + (l & 7),
+      // dims 16 n2 + 8 (l >> 4): registers {0, 1} = n-tile 2 n2, {2, 3} = n-tile 2 n2 + 1
+      const uint32_t vbase = smem_u32(&sm.v[st][p0 + 8 * ((lane >> 3) & 1) + (lane & 7)][8 * (lane >> 4)]);
+#pragma unroll
+      for (int n2 = 0; n2 < 4; ++n2) {
+        uint32_t vb[4];
+        ab_ldmatrix_x4_trans(vb, vbase + n2 * 32);
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+          float (&acc)[4] = o[2 * n2 + h2];
+          acc[0] *= f; acc[1] *= f; acc[2] *= f; acc[3] *= f;
+          ab_mma(acc, pa0, pa1, pa2, pa3, vb[2 * h2], vb[2 * h2 + 1]);
+        }
       }
-      if (nj & 1) {
-        const float pa = sm.s[warp][nj - 1];
-        const uint32_t va = *reinterpret_cast<const uint32_t *>(&sm.v[st][nj - 1][2 * lane]);
-        a0 = fmaf(pa, bf16_lo(va), a0); a1 = fmaf(pa, bf16_hi(va), a1);
-      }
-      o0 = fmaf(o0, f, a0 + b0);
-      o1 = fmaf(o1, f, a1 + b1);
     }
-    __syncthreads();                                   // scores and this stage are free for the next slice
+    __syncthreads();                                   // this stage is free for the slice after next
+  }
+  // ---- merge the eight warps (disjoint positions), in warp order; the staging area is the idle K stage
+  L += __shfl_xor_sync(0xffffffffu, L, 1);
+  L += __shfl_xor_sync(0xffffffffu, L, 2);
+  float *wo = reinterpret_cast<float *>(&sm.k[0][0][0]);       // [8 warps][8 heads][64]  (16 KB of the 18 KB stage)
+  float *wm = reinterpret_cast<float *>(&sm.s[0][0]);          // [8 warps][8 heads] maxima, then denominators
+  float *wl = wm + 64;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    *reinterpret_cast<float2 *>(wo + (warp * 8 + g) * 64 + 8 * i + 2 * c) = make_float2(o[i][0] + o[i][2], o[i][1] + o[i][3]);
+  }
+  if (c == 0) { wm[warp * 8 + g] = M; wl[warp * 8 + g] = L; }
+  __syncthreads();
+  float o0 = 0.f, o1 = 0.f;
+  M = -INFINITY; L = 0.f;
+  {
+    // thread = (head `warp`, dims 2 lane, 2 lane + 1), as the code below expects
+#pragma unroll
+    for (int w = 0; w < 8; ++w) M = fmaxf(M, wm[w * 8 + warp]);
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      const float mw = wm[w * 8 + warp];
+      const float fw = mw == -INFINITY ? 0.f : __expf(mw - M);
+      const float2 ov = *reinterpret_cast<const float2 *>(wo + (w * 8 + warp) * 64 + 2 * lane);
+      L = fmaf(wl[w * 8 + warp], fw, L);
+      o0 = fmaf(ov.x, fw, o0);
+      o1 = fmaf(ov.y, fw, o1);
+    }
   }
   const int qh = kvh * G + warp;
   if (S == 1) {
