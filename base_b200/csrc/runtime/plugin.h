@@ -131,6 +131,8 @@ struct Launcher {
   bool ok = true;
   std::string err;
   int issued = 0;
+  int limit = -1;     // >= 0: only the first `limit` launches are issued (launch-ladder profiling)
+  int count = 0;      // launches asked for so far
   // Timing ablation only: B200_SKIP="first:period[,first:period...]" drops launch number
   // first, first+period, ... of this launcher; the step's results are then meaningless.
   bool skipped() {
@@ -148,6 +150,8 @@ struct Launcher {
   void operator()(const char *name, std::initializer_list<int32_t> bufs, const S &scalars, int gx, int gy,
                   int gz, int bx, int smem = 0, int flags = 0) {
     if (!ok || skipped()) return;
+    if (limit >= 0 && count >= limit) { ++count; return; }
+    ++count;
     std::vector<int32_t> ids(bufs);
     int rc = cl_b200_launch(ctx, module, reinterpret_cast<const uint8_t *>(name), int32_t(ids.size()),
                             reinterpret_cast<const uint8_t *>(ids.data()),

@@ -132,6 +132,38 @@ class GptOss:
             raise RuntimeError(lib().cl_b200_last_error().decode())
         return buf.raw
 
+    # ---- graph capture / replay and the launch ladder (the reference's `capture`, `replay*`, `runTo{k}` extras:
+    # lean/algorithms/MlpCifarAlgorithm.lean:2233-2264, applications/ten-qwen/profile.py:34-36, 67-90)
+    def capture(self) -> int:
+        """Capture the step's CUDA graph without running it; returns the launches per step."""
+        out = bytearray(4)
+        self.base.execute_into(self.art.extras["capture"], b"", out)
+        return struct.unpack("<I", bytes(out))[0]
+
+    def replay(self, n: int = 1) -> float:
+        """n launches of the captured graph on whatever tokens / positions the device holds; ms (device events)."""
+        out = bytearray(4)
+        self.base.execute_into(self.art.extras["replay"], struct.pack("<I", n), out)
+        return struct.unpack("<f", bytes(out))[0]
+
+    def run_to(self, k: int) -> float:
+        """The first k launches of the step issued directly (no graph), one sync; ms (device events)."""
+        out = bytearray(4)
+        self.base.execute_into(self.art.extras["runTo"], struct.pack("<I", k), out)
+        return struct.unpack("<f", bytes(out))[0]
+
+    def launch_ladder(self, rungs, reps: int = 20) -> list:
+        """The reference's launch-ladder profile (profile.py:67-82): time prefixes of the launch sequence and
+        difference them.  Returns [(first, last, cumulative_us, bucket_us, us_per_launch)] per rung."""
+        rows, prev_k, prev_t = [], 0, 0.0
+        for k in rungs:
+            for _ in range(3):
+                self.run_to(k)
+            t = min(self.run_to(k) for _ in range(reps)) * 1e3
+            rows.append((prev_k, k, t, t - prev_t, (t - prev_t) / max(k - prev_k, 1)))
+            prev_k, prev_t = k, t
+        return rows
+
     STATE = dict(h1=0, xn=1, router_logits=2, topk_idx=3, topk_w=4, act=5, o=6, qkv=7, attn=8, y_part=9, route=10)
 
     def state(self, name: str, count: int, dtype="<f4") -> np.ndarray:

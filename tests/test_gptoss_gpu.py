@@ -292,3 +292,28 @@ def test_bad_requests_are_reported():
     with pytest.raises(RuntimeError, match="out of range"):
         m.infer([1], [c.max_seq])
     m.close()
+
+
+@pytest.mark.parametrize("flags", STEP_FLAGS)
+def test_capture_replay_and_the_launch_ladder(flags):
+    """The reference's graph extras (lean/algorithms/MlpCifarAlgorithm.lean:2233-2264) and its launch-ladder profile
+    (applications/ten-qwen/profile.py:67-90): a replayed graph gives bit-identical logits to the launched step, and the
+    cumulative time of the launch prefixes does not decrease."""
+    c = small(flags=flags)
+    a, b = GptOss(c), GptOss(c)
+    n = a.capture()
+    assert n == (1 if flags & PERSISTENT else 1 + c.layers * 6 + 2)
+    a.infer([7], [0])
+    ref = a.logits()[0].copy()
+    b.prep([7], [0])
+    assert b.replay(1) > 0
+    np.testing.assert_array_equal(b.logits()[0].view(np.uint32), ref.view(np.uint32))
+    b.prep([7], [0])
+    b.run_to(n)                                      # the same launches without the graph
+    np.testing.assert_array_equal(b.logits()[0].view(np.uint32), ref.view(np.uint32))
+    rungs = sorted({1, max(1, n // 2), n})
+    b.prep([7], [0])
+    rows = b.launch_ladder(rungs, reps=5)
+    assert [r[1] for r in rows] == rungs and all(r[2] > 0 for r in rows)
+    assert rows[-1][2] >= rows[0][2] * 0.8
+    a.close(), b.close()
