@@ -2,6 +2,8 @@
 synthetic tensors, the dequantised expert rows, greedy tokens wherever the
 oracle's top-2 logit margin exceeds the error bound.  Tolerance: logits
 max|d|/max|ref| <= 1e-3 (bf16 weights and KV, f32 accumulation, f32 activations)."""
+import struct
+
 import numpy as np
 import pytest
 
@@ -317,3 +319,34 @@ def test_capture_replay_and_the_launch_ladder(flags):
     assert [r[1] for r in rows] == rungs and all(r[2] > 0 for r in rows)
     assert rows[-1][2] >= rows[0][2] * 0.8
     a.close(), b.close()
+
+
+@pytest.mark.parametrize("flags", [pytest.param(PDL, id="per-op"), pytest.param(PDL | PERSISTENT | BLOCK_SCALED, id="persistent-block-scaled"),
+                                   pytest.param(PDL | 128, id="batched")])
+def test_weights_from_a_file_replace_the_seeded_ones(flags, tmp_path):
+    """base_b200/convert.py end to end: random tensors, experts quantised to MXFP4 by the converter, written as the flat
+    weight file, streamed into a loaded instance with `setTensor`, decoded, and compared with the oracle run on the
+    very same tensors."""
+    from base_b200 import convert as cv
+    from test_convert_cpu import random_weights
+    c = small(layers=2, flags=flags, batch=2 if flags & 128 else 1)
+    w = random_weights(c, seed=11)
+    path = tmp_path / "weights.bin"
+    cv.write_checkpoint(path, c, w)
+    m = GptOss(c)
+    before = m.infer([7] * c.batch, [0] * c.batch)
+    cv.load_checkpoint(m, path)
+    o = go.Model(ocfg(c), w=w)
+    tok = 7
+    for pos in range(6):
+        want, ref = o.step(tok, pos, return_logits=True)
+        got = m.infer([tok] * c.batch, [pos] * c.batch)
+        assert rel(m.logits()[0], ref) < TOL_LOGITS, f"pos {pos}"
+        top2 = np.sort(ref)[-2:]
+        if top2[1] - top2[0] > 4 * TOL_LOGITS * np.abs(ref).max():
+            assert int(got[0]) == want
+        tok = want
+    assert before is not None
+    with pytest.raises(RuntimeError, match="expected"):
+        m.base.execute(m.art.extras["setTensor"], struct.pack("<2I", 0, 0) + b"\0" * 12)
+    m.close()
