@@ -100,6 +100,9 @@ def lib() -> ctypes.CDLL:
     sig("cl_b200_comm_world", i32, vp)
     sig("cl_b200_comm_all_gather", i32, vp, i32, i64, i32, i64, i32)
     sig("cl_b200_comm_all_to_all", i32, vp, i32, i32, i64, i32)
+    sig("cl_b200_ipc_export", i32, vp, i32, vp)
+    sig("cl_b200_ipc_open", i64, vp, vp)
+    sig("cl_b200_ipc_close", i32, vp, i64)
     sig("cl_b200_last_error", cp)
     sig("cl_b200_argmax_noalloc", i32, vp, i32, i32, i32, vp, vp)
     sig("cl_b200_argmax_noalloc_error", cp)

@@ -811,6 +811,39 @@ int32_t cl_b200_comm_init(B200CudaContext *c, const uint8_t *id128, int32_t rank
   return 0;
 }
 
+int32_t cl_b200_ipc_export(B200CudaContext *c, int32_t buf_id, uint8_t *out64) {
+  if (!c || !out64) { set_err("ipc_export: null argument"); return -1; }
+  std::lock_guard<std::mutex> g(c->mu);
+  if (!bind(c)) return -1;
+  Buffer *b = get_buf(c, buf_id);
+  if (!b) { set_err("ipc_export: bad buffer"); return -1; }
+  CUipcMemHandle h;
+  static_assert(sizeof(h) == 64, "the handle is 64 bytes");
+  CU_TRY(c, g_drv.p_cuIpcGetMemHandle(&h, b->ptr));
+  memcpy(out64, &h, 64);
+  return 0;
+}
+
+int64_t cl_b200_ipc_open(B200CudaContext *c, const uint8_t *handle64) {
+  if (!c || !handle64) { set_err("ipc_open: null argument"); return 0; }
+  std::lock_guard<std::mutex> g(c->mu);
+  if (!bind(c)) return 0;
+  CUipcMemHandle h;
+  memcpy(&h, handle64, 64);
+  CUdeviceptr p = 0;
+  const CUresult r = g_drv.p_cuIpcOpenMemHandle(&p, h, CU_IPC_MEM_LAZY_ENABLE_PEER_ACCESS);
+  if (r != CUDA_SUCCESS) { set_err("cuIpcOpenMemHandle: " + cu_err(r)); return 0; }
+  return int64_t(p);
+}
+
+int32_t cl_b200_ipc_close(B200CudaContext *c, int64_t address) {
+  if (!c || address == 0) { set_err("ipc_close: null argument"); return -1; }
+  std::lock_guard<std::mutex> g(c->mu);
+  if (!bind(c)) return -1;
+  CU_TRY(c, g_drv.p_cuIpcCloseMemHandle(CUdeviceptr(address)));
+  return 0;
+}
+
 int32_t cl_b200_comm_world(B200CudaContext *c) { return c && c->comm ? c->comm_world : 1; }
 
 // recv[r * bytes .. (r + 1) * bytes) on every rank = rank r's send[send_offset .. + bytes).

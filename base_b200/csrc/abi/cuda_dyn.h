@@ -21,7 +21,8 @@
   X(cuGraphExecDestroy) X(cuGraphDestroy) X(cuMemAllocHost) X(cuMemFreeHost)    \
   X(cuModuleLoadData) X(cuModuleGetFunction) X(cuModuleUnload)                  \
   X(cuLaunchKernel) X(cuLaunchKernelEx) X(cuFuncSetAttribute)                   \
-  X(cuGetErrorString) X(cuMemHostRegister) X(cuMemHostUnregister)
+  X(cuGetErrorString) X(cuMemHostRegister) X(cuMemHostUnregister)          \
+  X(cuIpcGetMemHandle) X(cuIpcOpenMemHandle) X(cuIpcCloseMemHandle)
 
 // cuda.h maps the unversioned names to their current _vN symbols with
 // macros; stringify AFTER that expansion so dlsym asks for the right one.

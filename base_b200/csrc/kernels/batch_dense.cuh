@@ -50,11 +50,9 @@ struct RowsToAArgs { int K, B, mode, n_parts; long long part_stride; float eps; 
 
 B200_DEVICE uint16_t bd_bf16(float f) { return f32_to_bf16_rne(f); }
 
-extern "C" __global__ void __launch_bounds__(256)
-rows_to_a(const float *__restrict__ in, const float *__restrict__ parts, const float *__restrict__ w,
-          float *__restrict__ hout, float *__restrict__ xn, uint16_t *__restrict__ a_tiled, RowsToAArgs a) {
-  pdl_wait();
-  pdl_launch_dependents();
+B200_DEVICE void rows_to_a_body(const float *__restrict__ in, const float *__restrict__ parts, const float *__restrict__ w,
+                                float *__restrict__ hout, float *__restrict__ xn, uint16_t *__restrict__ a_tiled,
+                                const RowsToAArgs &a) {
   __shared__ float red[8];
   const int t = blockIdx.x, tid = threadIdx.x, K = a.K;
   const int nchunks = K >> 6;
@@ -113,6 +111,14 @@ rows_to_a(const float *__restrict__ in, const float *__restrict__ parts, const f
       *reinterpret_cast<uint2 *>(base + (kBdTokens + r) * 16) = make_uint2(uint32_t(lo[0]) | (uint32_t(lo[1]) << 16), uint32_t(lo[2]) | (uint32_t(lo[3]) << 16));
     }
   }
+}
+
+extern "C" __global__ void __launch_bounds__(256)
+rows_to_a(const float *__restrict__ in, const float *__restrict__ parts, const float *__restrict__ w,
+          float *__restrict__ hout, float *__restrict__ xn, uint16_t *__restrict__ a_tiled, RowsToAArgs a) {
+  pdl_wait();
+  pdl_launch_dependents();
+  rows_to_a_body(in, parts, w, hout, xn, a_tiled, a);
 }
 
 // ---- the GEMM -----------------------------------------------------------------------------------------

@@ -270,15 +270,13 @@ moe_prefill_down(const uint4 *__restrict__ tcodes, const uint32_t *__restrict__ 
 // divided among grid.y CTAs: many-token callers use grid.y = 1, the batched decode step grid.y = E / 8)
 struct RouterManyArgs { int T, H, E; };
 
-extern "C" __global__ void __launch_bounds__(256)
-moe_router_many(const float *__restrict__ Wr, const float *__restrict__ br, const float *__restrict__ x,
-                float *__restrict__ logits, RouterManyArgs a) {
-  pdl_wait();
-  pdl_launch_dependents();
+B200_DEVICE void router_many_body(const float *__restrict__ Wr, const float *__restrict__ br, const float *__restrict__ x,
+                                  float *__restrict__ logits, const RouterManyArgs &a) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int t0 = blockIdx.x * 4, nt = min(4, a.T - t0), n4 = a.H >> 2;
   float4 *xs = reinterpret_cast<float4 *>(dyn_smem);            // [4][H]
-  for (int i = tid; i < nt * n4; i += 256) xs[i] = __ldg(reinterpret_cast<const float4 *>(x + size_t(t0) * a.H) + i);
+  // x may have been written by another GPU while this kernel waited: read it through L2, not the read-only path
+  for (int i = tid; i < nt * n4; i += 256) xs[i] = __ldcg(reinterpret_cast<const float4 *>(x + size_t(t0) * a.H) + i);
   __syncthreads();
   for (int e = warp + 8 * blockIdx.y; e < a.E; e += 8 * gridDim.y) {      // grid.y CTAs share the experts
     const float4 *w4 = reinterpret_cast<const float4 *>(Wr + size_t(e) * a.H);
@@ -301,6 +299,14 @@ moe_router_many(const float *__restrict__ Wr, const float *__restrict__ br, cons
       logits[size_t(t0 + lane) * a.E + e] = v + br[e];
     }
   }
+}
+
+extern "C" __global__ void __launch_bounds__(256)
+moe_router_many(const float *__restrict__ Wr, const float *__restrict__ br, const float *__restrict__ x,
+                float *__restrict__ logits, RouterManyArgs a) {
+  pdl_wait();
+  pdl_launch_dependents();
+  router_many_body(Wr, br, x, logits, a);
 }
 
 // Routing tables and the token-tile list for A = T * top_k assignments, one CTA of 1024 threads.

@@ -93,6 +93,13 @@ struct BatchMxArgs { MoeDims d; int lo, n, P; };
 struct RouterManyArgs { int T, H, E; };
 struct TablesManyArgs { int A, E, lo, n; };
 struct CombineRangeArgs { int H, top_k, lo, n; };
+// peer_xchg.cuh: the exchange done by the kernels themselves over peer memory
+constexpr int kPeerMax = 8;
+struct PeerTable { unsigned long long xn_all[kPeerMax], y_recv[kPeerMax], flags[kPeerMax]; int rank, world; };
+struct RowsToPeersArgs { int K, B, tag; float eps; };
+struct RouterPeerArgs { RouterManyArgs r; int tag; };
+struct CombinePeersArgs { int H, top_k, lo, n, B, tag; };
+struct RowsToAPeerArgs { RowsToAArgs r; int tag; };
 struct RetileSegArgs { int R, K, n_mat; };
 constexpr int kBdThreads = 192, kBdSmemBytes = 6 * (8192 + 16 * 1024) + 64 * 129 * 4 + 512;
 constexpr int kBmThreads = 192, kBmSmemBytes = 8 * (16 * (8 * 128 + 64) + 8 * 8 * 128) + 192 * 8 + 4096;
@@ -132,6 +139,8 @@ struct State {
   // batched mode
   int batched = 0, lm_head_t = -1, a_tiled = -1, xn_all = -1, dig = -1, em = -1, y_part = -1, y_recv = -1, tiles = -1;
   int ep_rank = 0, ep_world = 1, expert_lo = 0, expert_n = 0, m64_rows16 = 1;
+  int peer = 0, peer_tab = -1, xflags = -1;      // peerInit: the kernels exchange over peer memory (no NCCL in the step)
+  std::vector<int64_t> peer_maps;               // addresses cl_b200_ipc_open returned
   LoadScope scope;
   int fail_after = -1;
   std::vector<int64_t> next_pos;     // per sequence: the position the next step will run at (-1: prep has not run)

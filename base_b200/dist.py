@@ -77,6 +77,14 @@ class Ranks:
         self._dist.broadcast_object_list(box, src=0)
         return box[0]
 
+    def all_gather_bytes(self, payload: bytes) -> list:
+        """Every rank's bytes on every rank, in rank order (the memory handles for GptOss.peer_init)."""
+        if self._dist is None:
+            return [payload]
+        box = [None] * self.world
+        self._dist.all_gather_object(box, payload)
+        return box
+
     def all_gather_rows(self, rows):
         """numpy [n, H] per rank -> [world * n, H], rank order (host path of the dispatch)."""
         if self._dist is None:

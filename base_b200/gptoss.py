@@ -123,6 +123,52 @@ class GptOss:
         with `new_comm_id()` and sent to every rank.  After construction, before the first step."""
         self.base.execute(self.art.extras["commInit"], comm_id)
 
+    def peer_handles(self) -> bytes:
+        """192 bytes: the handles of this rank's three exchange buffers (BATCHED, 2..8 ranks)."""
+        out = bytearray(192)
+        self.base.execute_into(self.art.extras["peerHandles"], b"", out)
+        return bytes(out)
+
+    def peer_init(self, handles) -> None:
+        """`handles`: every rank's `peer_handles()` in rank order.  From here on the step's dispatch and combine are
+        stores into the other ranks' memory by the kernels themselves (no NCCL call in the step); every rank calls
+        it, after construction and before the first step."""
+        self.base.execute(self.art.extras["peerInit"], b"".join(handles))
+        self._peer = True
+
+    def exchange_init(self, ranks, mode: str = "peer") -> str:
+        """Set up the step's exchange over `ranks` (a base_b200.dist.Ranks): "peer" (kernels store to peer memory;
+        falls back to NCCL when the ranks cannot map each other's memory) or "nccl".  Returns the mode in use."""
+        if ranks.world < 2:
+            return "none"
+        if mode == "peer" and ranks.world <= 8:
+            try:
+                mine, why = self.peer_handles(), ""
+            except RuntimeError as e:
+                mine, why = b"", str(e)
+            every = ranks.all_gather_bytes(mine)
+            if all(len(h) == 192 for h in every):
+                try:
+                    self.peer_init(every)
+                except RuntimeError as e:
+                    why = str(e)
+            else:
+                why = why or "a rank could not export its buffers"
+            if all(not w for w in ranks.all_gather_bytes(why.encode())):
+                return "peer"
+            if getattr(self, "_peer", False):
+                raise RuntimeError("peer memory was mapped on this rank but not on every rank")
+        self.comm_init(ranks.broadcast_bytes(GptOss.new_comm_id() if ranks.rank == 0 else None))
+        return "nccl"
+
+    def exchange_close(self, ranks) -> None:
+        """Unmap the other ranks' memory and meet them, so that no rank frees a buffer another still maps.  Call on
+        every rank before `close()` when `exchange_init` returned "peer" (harmless otherwise)."""
+        if getattr(self, "_peer", False):
+            self.base.execute(self.art.extras["peerClose"], b"")
+            self._peer = False
+        ranks.barrier()
+
     @staticmethod
     def new_comm_id() -> bytes:
         import ctypes

@@ -272,7 +272,7 @@ def run_qwen2(a, rank: int):
                          "achieved": step_bytes / step_s / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": step_bytes / step_s / 1e9 / peak, "peak_source": peak_kind, "traffic": None,
                          "bytes_per_launch": step_bytes, "us_per_launch": step_s * 1e6}}
-    print(json.dumps(line))
+    emit_line(line)
 
 
 def run_prefill(a, rank: int):
@@ -338,7 +338,7 @@ def run_prefill(a, rank: int):
                              "frac": flops / step_s / 1e12 / world / peak, "peak_source": kind, "traffic": None},
                 "finite": bool(np.isfinite(y).all())}
         if ranks.rank == 0:
-            print(json.dumps(line))
+            emit_line(line)
         ranks.close()
         return
     if rank != 0:
@@ -376,10 +376,30 @@ def run_prefill(a, rank: int):
                          "frac": flops / step_s / 1e12 / peak, "peak_source": kind, "traffic": None,
                          "flops_per_launch": flops, "us_per_launch": step_s * 1e6},
             "finite": bool(np.isfinite(y).all())}
-    print(json.dumps(line))
+    emit_line(line)
+
+
+_REAL_STDOUT = None
+
+
+def quiet_stdout():
+    """Libraries under this process (NCCL prints its version line) write to file descriptor 1; the contract is ONE JSON
+    line on stdout.  Point descriptor 1 at stderr for the run and keep the real one for `emit_line`."""
+    global _REAL_STDOUT
+    if _REAL_STDOUT is None:
+        sys.stdout.flush()
+        _REAL_STDOUT = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit_line(line: dict) -> None:
+    out = _REAL_STDOUT or sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
 
 
 def main():
+    quiet_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
@@ -400,6 +420,8 @@ def main():
     ap.add_argument("--workload", choices=("gptoss", "gptoss120b", "qwen2", "prefill"), default="gptoss",
                     help="gptoss: BASELINE config 3 (the headline); qwen2: BASELINE config 1 (Qwen2-0.5B f32, single GPU); "
                          "prefill: BASELINE config 2 (one MoE layer, 2048 tokens, tensor cores)")
+    ap.add_argument("--exchange", choices=("peer", "nccl"), default="peer",
+                    help="N > 1: the step's dispatch and combine as stores into peer memory by the kernels themselves, or NCCL")
     ap.add_argument("--step", choices=("persistent", "per-op"), default="persistent",
                     help="one persistent kernel per decode step (default) or one launch per operation")
     ap.add_argument("--experts", choices=("block-scaled", "cuda-core"), default="block-scaled",
@@ -459,7 +481,7 @@ def run_batch1(a, rank: int, world: int, local: int, ranks=None, emit: bool = Tr
                 "vs_baseline": None, "dtype": "mxfp4 weights, f32 accumulate", "data": "synthetic",
                 "config": config, "impl": "reference", "cpu_baseline": base,
                 "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-        print(json.dumps(line))
+        emit_line(line)
         return
 
     from base_b200.dist import Ranks
@@ -571,7 +593,7 @@ def run_batch1(a, rank: int, world: int, local: int, ranks=None, emit: bool = Tr
     m.close()
     if rank == 0 and emit:
         line["cpu_baseline"] = cpu_baseline(cfg, a.prompt)
-        print(json.dumps(line))
+        emit_line(line)
     if own_ranks:
         ranks.close()
     return line
@@ -605,8 +627,7 @@ def run_batched(a, rank: int, world: int, local: int):
                           f", greedy (BASELINE config {'4' if big else '3'}, batch {Bg})",
               "layers": cfg.layers, "hidden": cfg.hidden, "experts": cfg.experts, "top_k": cfg.top_k, "vocab": cfg.vocab,
               "context": a.prompt, "global_batch": Bg, "batch_per_gpu": per,
-              "parallelism": (f"expert parallel x{world} (experts {cfg.experts // world} per GPU, NCCL all-gather + all-to-all per "
-                              f"layer), sequences and attention data parallel x{world}") if world > 1 else "single GPU",
+              "parallelism": f"expert parallel x{world}" if world > 1 else "single GPU",
               "step": "one CUDA graph per step: tcgen05 skinny GEMMs (dense), block-scaled tcgen05 expert kernel, split-KV attention",
               "l2": "each step streams >= 3.7 GB of weights per GPU, far larger than L2; no flush needed"}
     if a.impl == "reference":
@@ -627,14 +648,19 @@ def run_batched(a, rank: int, world: int, local: int):
                 "scaling": "strong", "vs_baseline": None, "dtype": "mxfp4 weights, f32 accumulate", "data": "synthetic",
                 "config": config, "impl": "reference", "cpu_baseline": base,
                 "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-        print(json.dumps(line))
+        emit_line(line)
         return
 
     ranks = Ranks("nccl" if world > 1 else None)
     barrier, max_over_ranks = ranks.barrier, ranks.max
     m = GptOss(cfg)
+    exchange = m.exchange_init(ranks, a.exchange)
     if world > 1:
-        m.comm_init(ranks.broadcast_bytes(GptOss.new_comm_id() if rank == 0 else None))
+        how = ("dispatch and combine fused into the producing kernels as NVLink stores into the peers' memory, flag waits in the "
+               "consumers" if exchange == "peer" else "NCCL all-gather + all-to-all per layer inside the graph")
+        config["parallelism"] = (f"expert parallel x{world} (experts {cfg.experts // world} per GPU; {how}), sequences and "
+                                 f"attention data parallel x{world}")
+        config["exchange"] = exchange
     rng = np.random.default_rng(1000 * 3 + 17)
     if a.synthetic_kv:
         m.fill_kv()
@@ -707,9 +733,10 @@ def run_batched(a, rank: int, world: int, local: int):
             "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "mxfp4 experts / bf16 dense weights, f32 accumulate", "data": "synthetic", "config": config,
             "e2e": {"value": Bg * a.steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 8 * per, "d2h_bytes_per_step": 4 * per},
-            "gpu_launches": a.steps * len(rep_ms) * launches_per_step, "clocks": clocks, "roofline": roof,
+            "gpu_launches": a.steps * len(rep_ms) * (launches_per_step + (1 if exchange == "peer" else 0)), "clocks": clocks, "roofline": roof,
             "repeats": {"n": len(rep_ms), "ms_per_step": [round(r / a.steps, 5) for r in rep_ms], "reported": "median",
                         "min_tokens_per_s": Bg * a.steps / (max(rep_ms) * 1e-3), "max_tokens_per_s": Bg * a.steps / (min(rep_ms) * 1e-3)}}
+    m.exchange_close(ranks)
     m.close()
     if world == 1 and not a.no_batch1 and not big:
         # the batch-1 workload of the same config on the same GPU: the persistent step kernel
@@ -718,7 +745,7 @@ def run_batched(a, rank: int, world: int, local: int):
         line["batch1"]["config"] = b1["config"]
     if rank == 0:
         line["cpu_baseline"] = cpu_baseline(dataclasses.replace(model), a.prompt)
-        print(json.dumps(line))
+        emit_line(line)
     ranks.close()
 
 

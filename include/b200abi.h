@@ -208,6 +208,17 @@ int32_t cl_b200_comm_all_gather(B200CudaContext *ctx, int32_t send_buf, int64_t 
 int32_t cl_b200_comm_all_to_all(B200CudaContext *ctx, int32_t send_buf, int32_t recv_buf, int64_t bytes,
                                 int32_t stream_id);
 
+/* Peer memory, for kernels that write to and read from another process's buffers over NVLink themselves
+ * (the batched decode step's dispatch and combine).  No counterpart in the reference (cuda.rs has one
+ * device per process and no inter-process memory).  export: a 64-byte handle of a buffer made by
+ * cl_cuda_create_buffer; open: the address, in this process, of the buffer behind a handle another process
+ * exported (peer access is enabled by the call); close: unmaps it.  Handles travel by any host channel.
+ * The exported buffer must outlive every mapping of it.  open returns 0 on error. */
+int32_t cl_b200_ipc_export(B200CudaContext *ctx, int32_t buf_id, uint8_t *out64);
+int64_t cl_b200_ipc_open(B200CudaContext *ctx, const uint8_t *handle64);
+int32_t cl_b200_ipc_close(B200CudaContext *ctx, int64_t address);
+
+
 /* Last error text of the calling thread ("" if none); never null. */
 const char *cl_b200_last_error(void);
 

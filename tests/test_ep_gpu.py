@@ -1,5 +1,6 @@
-"""Expert-parallel batched decode on two GPUs (one process per GPU, NCCL all-gather + all-to-all inside the
-step's CUDA graph) against the same batch on one GPU.  Skipped where fewer than two GPUs are visible."""
+"""Expert-parallel batched decode on two GPUs (one process per GPU) against the same batch on one GPU, with both
+forms of the exchange: the kernels' own stores into peer memory, and NCCL all-gather + all-to-all inside the step's
+CUDA graph.  Skipped where fewer than two GPUs are visible."""
 import os
 import socket
 
@@ -32,7 +33,7 @@ FIRSTS = [7, 99, 400, 3, 250, 31]
 STEPS = 10
 
 
-def _worker(rank: int, world: int, port: int, out):
+def _worker(rank: int, world: int, port: int, out, exchange: str):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
                       MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     from base_b200.dist import Ranks
@@ -40,7 +41,7 @@ def _worker(rank: int, world: int, port: int, out):
     r = Ranks(backend="gloo")
     per = len(FIRSTS) // world
     m = GptOss(GptOssConfig(**CFG, batch=per, flags=PDL | BATCHED, ep_rank=rank, ep_world=world))
-    m.comm_init(r.broadcast_bytes(GptOss.new_comm_id() if rank == 0 else None))
+    used = m.exchange_init(r, exchange)
     toks = FIRSTS[rank * per:(rank + 1) * per]
     hist, logit_hist = [], []
     for pos in range(STEPS):
@@ -49,26 +50,42 @@ def _worker(rank: int, world: int, port: int, out):
         logit_hist.append(m.logits().copy())
         hist.append(got.tolist())
         toks = [int(t) for t in got]
-    out.put((rank, hist, np.stack(logit_hist)))
-    r.barrier()
+    late = ""
+    if used == "peer":
+        # rank 0 runs one more step alone: the flag it waits for is never set, the wait runs out and the step
+        # reports it (the context stays usable: close() below frees everything)
+        r.barrier()
+        if rank == 0:
+            try:
+                m.infer(toks, [STEPS] * per)
+                late = "no error"
+            except RuntimeError as e:
+                late = str(e)
+    out.put((rank, hist, np.stack(logit_hist), used, late))
+    m.exchange_close(r)
     m.close()
     r.close()
 
 
 @pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
-def test_two_gpu_expert_parallel_decode_equals_one_gpu():
+@pytest.mark.parametrize("exchange", ["peer", "nccl"])
+def test_two_gpu_expert_parallel_decode_equals_one_gpu(exchange):
     import torch.multiprocessing as mp
     from base_b200.gptoss import GptOss, GptOssConfig, PDL, BATCHED
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, out, exchange)) for r in range(2)]
     for p in procs:
         p.start()
     got = sorted(out.get(timeout=600) for _ in procs)
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
+    assert all(g[3] == exchange for g in got), [g[3] for g in got]
+    if exchange == "peer":
+        assert "4001" in got[0][4] or "4002" in got[0][4], got[0][4]      # the wait ran out and said so
+    got = [g[:3] for g in got]
     one = GptOss(GptOssConfig(**CFG, batch=len(FIRSTS), flags=PDL | BATCHED))
     toks = list(FIRSTS)
     per = len(FIRSTS) // 2
