@@ -66,10 +66,23 @@ B200_DEVICE void ab_ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
 // Warp w owns positions [16 w, 16 w + 16) of every slice, for all q heads of the group: Q K^T is two n-tiles x four
 // k-steps, P V one k-step x eight n-tiles; its running maximum, denominator and output stay in registers over the
 // slices and the eight warps are merged once at the end, in warp order.
+// The o-proj's A operand (rows_to_a, mode 0, of batch_dense.cuh) written by the attention itself: elements k, k + 1 of
+// sequence b as the hi / lo bf16 rows r and Rh + r of the tile [pass][K chunk = q head][column group][2 Rh rows][16 B].
+B200_DEVICE void attn_store_a(uint16_t *a_tiled, int b, int B, int NQ, int qh, int lane, float x0, float x1) {
+  const int pass = b >> 5, r = b & 31, cg = lane >> 2, e = (2 * lane) & 7;
+  const uint16_t h0 = f32_to_bf16_rne(x0), h1 = f32_to_bf16_rne(x1);
+  const uint16_t l0 = f32_to_bf16_rne(x0 - bf16_lo(uint32_t(h0))), l1 = f32_to_bf16_rne(x1 - bf16_lo(uint32_t(h1)));
+  const int Rh = B >= 32 ? 32 : ((B + 7) & ~7);                   // bd_rh of batch_dense.cuh
+  uint8_t *base = reinterpret_cast<uint8_t *>(a_tiled) + ((size_t(pass) * NQ + qh) * 8 + cg) * (2 * Rh * 16) + e * 2;
+  *reinterpret_cast<uint32_t *>(base + r * 16) = uint32_t(h0) | (uint32_t(h1) << 16);
+  *reinterpret_cast<uint32_t *>(base + (Rh + r) * 16) = uint32_t(l0) | (uint32_t(l1) << 16);
+}
+
 extern "C" __global__ void __launch_bounds__(kAbThreads, 2)
 attn_decode_batch(const float *__restrict__ qkv, const float *__restrict__ rope, const int *__restrict__ meta,
                   uint16_t *kcache, uint16_t *vcache, const float *__restrict__ sinks, float *__restrict__ part_o,
-                  float *__restrict__ part_ml, int *__restrict__ counters, float *__restrict__ attn_out, AttnBatchArgs a) {
+                  float *__restrict__ part_ml, int *__restrict__ counters, float *__restrict__ attn_out,
+                  uint16_t *__restrict__ a_tiled, AttnBatchArgs a) {
   AttnBatchSmem &sm = *reinterpret_cast<AttnBatchSmem *>(dyn_smem);
   constexpr int HD = 64, HALF = 32;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -246,6 +259,7 @@ attn_decode_batch(const float *__restrict__ qkv, const float *__restrict__ rope,
       const float Mf = fmaxf(M, sk), f = __expf(M - Mf);
       const float Lf = fmaf(L, f, __expf(sk - Mf));
       *reinterpret_cast<float2 *>(attn_out + size_t(b) * QD + size_t(qh) * HD + 2 * lane) = make_float2(o0 * f / Lf, o1 * f / Lf);
+      if (a_tiled) attn_store_a(a_tiled, b, a.B, a.NQ, qh, lane, o0 * f / Lf, o1 * f / Lf);
     }
     return;
   }
@@ -280,5 +294,6 @@ attn_decode_batch(const float *__restrict__ qkv, const float *__restrict__ rope,
     }
     Lm += __expf(__ldg(sinks + qh) - Mm);
     *reinterpret_cast<float2 *>(attn_out + size_t(b) * QD + size_t(qh) * HD + 2 * lane) = make_float2(m0 / Lm, m1 / Lm);
+    if (a_tiled) attn_store_a(a_tiled, b, a.B, a.NQ, qh, lane, m0 / Lm, m1 / Lm);
   }
 }

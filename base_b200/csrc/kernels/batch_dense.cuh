@@ -11,7 +11,7 @@
 // Layouts (made once: dense_tc_retile for weights, rows_to_a for activations):
 //   W tiled: [K chunk of 64][row group of 8][column group of 8 (16 B)][8 rows][16 B]  -> the row groups a CTA owns
 //            are one contiguous piece per chunk (one bulk copy into a ring slot);
-//   A tiled: [pass][K chunk of 64][column group][64 rows][16 B]                          -> 8 KB per pass and chunk.
+//   A tiled: [pass][K chunk of 64][column group][2 * bd_rh(B) rows][16 B]                -> 8 KB per pass and chunk at 32 tokens, less below.
 // Every wait is bounded; on timeout a code is stored in *status and the kernel ends.
 #pragma once
 #include "tc_gemm.cuh"
@@ -45,10 +45,17 @@ dense_tc_retile(const uint4 *__restrict__ src, uint4 *__restrict__ dst, DenseRet
 // mode 1: h = in[t] + sum_g parts[g][t] (g ascending; the experts' partial sums of every rank), hout[t] = h,
 //         x = h * inv * w, inv = 1 / sqrt(mean(h^2) + eps)  (combine + residual + RMSNorm -> qkv / lm_head)
 // mode 2: as mode 1 without parts and without the A operand: xn[t] = x only (RMSNorm -> router, experts)
+// mode 3: as mode 1 with the experts' combine done here (one GPU, every expert local): parts = the experts' outputs
+//         o[t * n_parts + j], xn = the routing weights w[t][j] (read only), n_parts = top_k;
+//         h = in[t] + sum_j w[t][j] * o[t * top_k + j], the sum folded in slot order from zero as moe_combine_range does
 // One CTA of 256 threads per token; K % 64 == 0, K <= 4096.
 struct RowsToAArgs { int K, B, mode, n_parts; long long part_stride; float eps; };
 
 B200_DEVICE uint16_t bd_bf16(float f) { return f32_to_bf16_rne(f); }
+// hi rows per pass: 32, or with fewer than 32 tokens their count rounded up to 8 (the A tile of a K chunk is then
+// [column group][2 * bd_rh rows][16 B]: fewer bytes for every CTA to copy; the instruction still reads 64 rows, what
+// lies behind the tile's rows gives accumulator rows nobody reads)
+B200_DEVICE int bd_rh(int B) { return B >= 32 ? 32 : ((B + 7) & ~7); }
 
 B200_DEVICE void rows_to_a_body(const float *__restrict__ in, const float *__restrict__ parts, const float *__restrict__ w,
                                 float *__restrict__ hout, float *__restrict__ xn, uint16_t *__restrict__ a_tiled,
@@ -69,7 +76,16 @@ B200_DEVICE void rows_to_a_body(const float *__restrict__ in, const float *__res
           const float4 p = __ldcg(reinterpret_cast<const float4 *>(parts + size_t(g) * a.part_stride + size_t(t) * K) + i4);
           x.x += p.x; x.y += p.y; x.z += p.z; x.w += p.w;
         }
-      if (a.mode == 1 && hout) reinterpret_cast<float4 *>(hout + size_t(t) * K)[i4] = x;
+      if (a.mode == 3) {                                      // the combine of moe_combine_range, then the residual
+        float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < a.n_parts; ++j) {
+          const float wj = __ldcg(xn + t * a.n_parts + j);
+          const float4 p = __ldcg(reinterpret_cast<const float4 *>(parts + size_t(t * a.n_parts + j) * K) + i4);
+          y.x = fmaf(wj, p.x, y.x); y.y = fmaf(wj, p.y, y.y); y.z = fmaf(wj, p.z, y.z); y.w = fmaf(wj, p.w, y.w);
+        }
+        x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+      }
+      if (a.mode != 0 && a.mode != 2 && hout) reinterpret_cast<float4 *>(hout + size_t(t) * K)[i4] = x;
     }
     v[4 * u] = x.x; v[4 * u + 1] = x.y; v[4 * u + 2] = x.z; v[4 * u + 3] = x.w;
     ss = fmaf(x.x, x.x, ss); ss = fmaf(x.y, x.y, ss); ss = fmaf(x.z, x.z, ss); ss = fmaf(x.w, x.w, ss);
@@ -89,7 +105,7 @@ B200_DEVICE void rows_to_a_body(const float *__restrict__ in, const float *__res
         const float4 g = __ldg(reinterpret_cast<const float4 *>(w) + i4);
         v[4 * u] = v[4 * u] * inv * g.x; v[4 * u + 1] = v[4 * u + 1] * inv * g.y;
         v[4 * u + 2] = v[4 * u + 2] * inv * g.z; v[4 * u + 3] = v[4 * u + 3] * inv * g.w;
-        if (xn) reinterpret_cast<float4 *>(xn + size_t(t) * K)[i4] = make_float4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
+        if (xn && a.mode != 3) reinterpret_cast<float4 *>(xn + size_t(t) * K)[i4] = make_float4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
       }
     }
   }
@@ -106,9 +122,10 @@ B200_DEVICE void rows_to_a_body(const float *__restrict__ in, const float *__res
         hi[j] = bd_bf16(v[4 * u + j]);
         lo[j] = bd_bf16(v[4 * u + j] - bf16_lo(uint32_t(hi[j])));
       }
-      uint8_t *base = reinterpret_cast<uint8_t *>(a_tiled) + ((size_t(pass) * nchunks + c) * 8 + cg) * (kBdRows * 16) + e * 2;
+      const int Rh = bd_rh(a.B);
+      uint8_t *base = reinterpret_cast<uint8_t *>(a_tiled) + ((size_t(pass) * nchunks + c) * 8 + cg) * (2 * Rh * 16) + e * 2;
       *reinterpret_cast<uint2 *>(base + r * 16) = make_uint2(uint32_t(hi[0]) | (uint32_t(hi[1]) << 16), uint32_t(hi[2]) | (uint32_t(hi[3]) << 16));
-      *reinterpret_cast<uint2 *>(base + (kBdTokens + r) * 16) = make_uint2(uint32_t(lo[0]) | (uint32_t(lo[1]) << 16), uint32_t(lo[2]) | (uint32_t(lo[3]) << 16));
+      *reinterpret_cast<uint2 *>(base + (Rh + r) * 16) = make_uint2(uint32_t(lo[0]) | (uint32_t(lo[1]) << 16), uint32_t(lo[2]) | (uint32_t(lo[3]) << 16));
     }
   }
 }
@@ -150,24 +167,25 @@ B200_DEVICE bool bd_wait(uint64_t *bar, uint32_t parity, BdBars *b, int *status,
   return false;
 }
 
-// Four K = 16 instructions over one K chunk of 64 (the operands advance by two column groups each: 2 x 64 rows x 16 B
-// of A, 2 x 128 B of B), issued by an elected lane of the converged warp.
+// Four K = 16 instructions over one K chunk of 64 (the operands advance by two column groups each: a_step 16-byte units
+// of A = 2 x (tile rows) x 16 B, 2 x 128 B of B), issued by an elected lane of the converged warp.
 // The four go to accumulators d_tmem + i * d_step (d_step = 0: one accumulator): with several accumulators the
 // instructions of a chunk do not wait for one another's results, the epilogue adds them up.
-B200_DEVICE void bd_mma4_warp(uint32_t d_tmem, uint32_t d_step, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool accumulate_first) {
+B200_DEVICE void bd_mma4_warp(uint32_t d_tmem, uint32_t d_step, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool accumulate_first,
+                              uint64_t a_step) {
   asm volatile(
       "{\n.reg .pred p, p1, e;\n.reg .b64 a1, a2, a3, b1, b2, b3;\n.reg .b32 d1, d2, d3;\n"
       "elect.sync _|e, 0xffffffff;\n"
       "setp.ne.b32 p, %4, 0;\n"
       "setp.eq.b32 p1, %5, 0;\nor.pred p1, p1, p;\n"          // later instructions accumulate unless they own a fresh accumulator
       "add.u32 d1, %0, %5;\nadd.u32 d2, d1, %5;\nadd.u32 d3, d2, %5;\n"
-      "add.u64 a1, %1, 128;\nadd.u64 a2, %1, 256;\nadd.u64 a3, %1, 384;\n"
+      "add.u64 a1, %1, %6;\nadd.u64 a2, a1, %6;\nadd.u64 a3, a2, %6;\n"
       "add.u64 b1, %2, 16;\nadd.u64 b2, %2, 32;\nadd.u64 b3, %2, 48;\n"
       "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
       "@e tcgen05.mma.cta_group::1.kind::f16 [d1], a1, b1, %3, p1;\n"
       "@e tcgen05.mma.cta_group::1.kind::f16 [d2], a2, b2, %3, p1;\n"
       "@e tcgen05.mma.cta_group::1.kind::f16 [d3], a3, b3, %3, p1;\n}\n" ::"r"(d_tmem),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(uint32_t(accumulate_first)), "r"(d_step)
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(uint32_t(accumulate_first)), "r"(d_step), "l"(a_step)
       : "memory");
 }
 
@@ -185,7 +203,9 @@ dense_tc_gemm(const uint8_t *__restrict__ Wt, const uint8_t *__restrict__ At, co
   const int g_lo = int((long long)RG * blockIdx.x / gridDim.x), g_hi = int((long long)RG * (blockIdx.x + 1) / gridDim.x);
   const int units = (g_hi - g_lo + kBdMaxGroups - 1) / kBdMaxGroups, jobs = units * passes;
   // few rows per CTA (qkv, o-proj): small slots, many of them in flight; many rows (lm_head): 6 slots of 24 KB
-  const uint32_t slot_bytes = 8192u + uint32_t(max(1, min(kBdMaxGroups, g_hi - g_lo))) * 1024u;
+  const int Rh = bd_rh(a.B);
+  const uint32_t a_bytes = 256u * uint32_t(Rh);                // the A tile of one pass and K chunk
+  const uint32_t slot_bytes = a_bytes + uint32_t(max(1, min(kBdMaxGroups, g_hi - g_lo))) * 1024u;
   const uint32_t n_slots = min(uint32_t(kBdSlots), uint32_t(kBdRingBytes) / slot_bytes);
   // every CTA reads the same A piece for a given K chunk: start each CTA at a different chunk, so that at any moment
   // the CTAs ask L2 for different lines (a CTA's own summation order stays fixed)
@@ -216,10 +236,10 @@ dense_tc_gemm(const uint8_t *__restrict__ Wt, const uint8_t *__restrict__ At, co
           const uint32_t s = q % n_slots;
           if (q >= n_slots && !bd_wait(&bars->empty[s], ((q / n_slots) - 1) & 1, bars, status, 61)) { j = jobs; break; }
           uint8_t *dst = ring + size_t(s) * slot_bytes;
-          mbar_expect_tx(&bars->full[s], 8192u + uint32_t(ng) * 1024u);
+          mbar_expect_tx(&bars->full[s], a_bytes + uint32_t(ng) * 1024u);
           const int cc = (c + c_off) % nchunks;
-          bulk_g2s(dst, At + (size_t(pass) * nchunks + cc) * 8192, 8192u, &bars->full[s]);
-          bulk_g2s(dst + 8192, Wt + (size_t(cc) * RG + g0) * 1024, uint32_t(ng) * 1024u, &bars->full[s]);
+          bulk_g2s(dst, At + (size_t(pass) * nchunks + cc) * a_bytes, a_bytes, &bars->full[s]);
+          bulk_g2s(dst + a_bytes, Wt + (size_t(cc) * RG + g0) * 1024, uint32_t(ng) * 1024u, &bars->full[s]);
         }
       }
     }
@@ -240,9 +260,9 @@ dense_tc_gemm(const uint8_t *__restrict__ Wt, const uint8_t *__restrict__ At, co
         ok = bd_wait(&bars->full[s], (q / n_slots) & 1, bars, status, 63);
         if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t sa = smem_u32(ring + size_t(s) * slot_bytes), sb = sa + 8192;
-        const uint64_t da = tc_smem_desc(sa, kBdRows * 16, 128), db = tc_smem_desc(sb, 128, 1024);
-        bd_mma4_warp(acc, d_step, da, db, idesc, c > 0);
+        const uint32_t sa = smem_u32(ring + size_t(s) * slot_bytes), sb = sa + a_bytes;
+        const uint64_t da = tc_smem_desc(sa, 2 * Rh * 16, 128), db = tc_smem_desc(sb, 128, 1024);
+        bd_mma4_warp(acc, d_step, da, db, idesc, c > 0, uint64_t(4 * Rh));
         tc_commit_warp(&bars->empty[s], true);
         tc_commit_warp(&bars->done[j & 1], c == nchunks - 1);
         __syncwarp();
@@ -280,7 +300,7 @@ dense_tc_gemm(const uint8_t *__restrict__ Wt, const uint8_t *__restrict__ At, co
       const int ntok = min(kBdTokens, a.B - pass * kBdTokens);
       for (int idx = tid; idx < ntok * N; idx += 128) {
         const int t = idx / N, n = idx % N, r = g0 * 8 + n;
-        float val = stage[t * kBdStageStride + n] + stage[(kBdTokens + t) * kBdStageStride + n];
+        float val = stage[t * kBdStageStride + n] + stage[(Rh + t) * kBdStageStride + n];
         if (bias) val += __ldg(bias + r);
         const size_t o = size_t(pass * kBdTokens + t) * a.out_stride + r;
         if (a.kind == 1) val += __ldcg(res + o);

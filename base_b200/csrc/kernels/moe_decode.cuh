@@ -81,12 +81,8 @@ moe_router_logits(const float *__restrict__ Wr, const float *__restrict__ br,
 // ---- top-k + softmax over the selected logits -----------------------------------
 // One warp per token.  E <= 128 (4 logits per lane).  Selection is by
 // (logit descending, expert id ascending); NaN logits sort last.
-extern "C" __global__ void __launch_bounds__(32)
-moe_topk_softmax(const float *__restrict__ logits, int *__restrict__ topk_idx,
-                 float *__restrict__ topk_w, MoeDims d) {
-  pdl_wait();
-  const int t = blockIdx.x;
-  const int lane = threadIdx.x;
+B200_DEVICE void topk_softmax_token(const float *__restrict__ logits, int *__restrict__ topk_idx,
+                                    float *__restrict__ topk_w, const MoeDims &d, int t, int lane) {
   float v[4];
   bool taken[4];
 #pragma unroll
@@ -127,6 +123,13 @@ moe_topk_softmax(const float *__restrict__ logits, int *__restrict__ topk_idx,
       topk_w[size_t(t) * d.top_k + j] = ex[j] / s;
     }
   }
+}
+
+extern "C" __global__ void __launch_bounds__(32)
+moe_topk_softmax(const float *__restrict__ logits, int *__restrict__ topk_idx,
+                 float *__restrict__ topk_w, MoeDims d) {
+  pdl_wait();
+  topk_softmax_token(logits, topk_idx, topk_w, d, blockIdx.x, threadIdx.x);
 }
 
 // ---- shared GEMV core: 16 rows x (K/32 block columns), one token ----------------

@@ -315,18 +315,16 @@ moe_router_many(const float *__restrict__ Wr, const float *__restrict__ br, cons
 // ascending, an expert's tiles in slot order.  E <= 128.
 struct TablesManyArgs { int A, E, lo, n; };   // token tiles only for experts [lo, lo + n) (expert-parallel ranks), numbered from lo
 
-extern "C" __global__ void __launch_bounds__(1024)
-moe_route_tables_many(const int *__restrict__ topk_idx, int *__restrict__ route, int *__restrict__ tiles,
-                      TablesManyArgs a) {
-  pdl_wait();
-  pdl_launch_dependents();
+// topk_idx may have been written by this CTA just before (moe_topk_tables_many): it is read through L2
+B200_DEVICE void route_tables_many_body(const int *topk_idx, int *__restrict__ route, int *__restrict__ tiles,
+                                        const TablesManyArgs &a) {
   const int A = a.A, E = a.E, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int *n_active = route, *count = route + 1, *offset = route + 1 + E, *active = offset + E + 1, *perm = active + E;
   __shared__ int s_count[128], s_offset[129], s_run[128];
   __shared__ int s_warp[32][128];          // per chunk: assignments of expert e in warp w
   if (tid < 128) { s_count[tid] = 0; s_run[tid] = 0; }
   __syncthreads();
-  for (int i = tid; i < A; i += 1024) atomicAdd(&s_count[topk_idx[i]], 1);      // integer counts: order-free
+  for (int i = tid; i < A; i += 1024) atomicAdd(&s_count[__ldcg(topk_idx + i)], 1);      // integer counts: order-free
   __syncthreads();
   if (tid == 0) {
     int run = 0, na = 0, nt = 0;
@@ -353,7 +351,7 @@ moe_route_tables_many(const int *__restrict__ topk_idx, int *__restrict__ route,
   // warps before this one in the chunk, then the chunks before (s_run)
   for (int base = 0; base < A; base += 1024) {
     const int i = base + tid;
-    const int e = i < A ? topk_idx[i] : -1;
+    const int e = i < A ? __ldcg(topk_idx + i) : -1;
     for (int j = tid; j < 32 * 128; j += 1024) (&s_warp[0][0])[j] = 0;
     __syncthreads();
     const unsigned same = __match_any_sync(0xffffffffu, e);
@@ -373,6 +371,29 @@ moe_route_tables_many(const int *__restrict__ topk_idx, int *__restrict__ route,
     }
     __syncthreads();
   }
+}
+
+extern "C" __global__ void __launch_bounds__(1024)
+moe_route_tables_many(const int *__restrict__ topk_idx, int *__restrict__ route, int *__restrict__ tiles,
+                      TablesManyArgs a) {
+  pdl_wait();
+  pdl_launch_dependents();
+  route_tables_many_body(topk_idx, route, tiles, a);
+}
+
+// Top-k + softmax (moe_topk_softmax, one warp per token) and the routing tables in ONE CTA of 1024 threads: the batched
+// decode step's form (a launch less per layer).  T = A / top_k tokens.
+struct TopkTablesArgs { MoeDims d; TablesManyArgs t; };
+
+extern "C" __global__ void __launch_bounds__(1024)
+moe_topk_tables_many(const float *__restrict__ logits, int *__restrict__ topk_idx, float *__restrict__ topk_w,
+                     int *__restrict__ route, int *__restrict__ tiles, TopkTablesArgs a) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int T = a.t.A / a.d.top_k;
+  for (int t = threadIdx.x >> 5; t < T; t += 32) topk_softmax_token(logits, topk_idx, topk_w, a.d, t, threadIdx.x & 31);
+  __syncthreads();                           // the tables below read topk_idx written by this CTA
+  route_tables_many_body(topk_idx, route, tiles, a.t);
 }
 
 // f32 rows -> bf16 (round to nearest even), 8 elements per thread.

@@ -94,7 +94,7 @@ def test_dense_gemm_accumulator_rows_and_numpy(ctx):
 
 
 @pytest.mark.parametrize("rows,K,B,kind,grid", [(5120, 2880, 32, 0, 148), (2880, 4096, 7, 1, 148), (4096, 2880, 70, 0, 37),
-                                                 (72, 64, 1, 1, 5)])
+                                                 (72, 64, 1, 1, 5), (2880, 4096, 12, 1, 148), (5120, 2880, 20, 0, 148)])
 def test_dense_gemm_shapes(ctx, rows, K, B, kind, grid):
     L, c = ctx
     out, ref = run_gemm(L, c, rows, K, B, kind, 1, grid, np.random.default_rng(rows + K + B))

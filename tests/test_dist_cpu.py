@@ -116,6 +116,8 @@ def _ep_worker(rank: int, world: int, port: int, out):
     y = ep_moe_layer(r, mine, cfg.experts, cfg.top_k, route, expert)
     want = mo.moe_ffn(x_all, p)[rank * 3:(rank + 1) * 3]
     lo, n = expert_range(rank, world, cfg.experts)
+    handles = r.all_gather_bytes(b"handles-of-%d" % rank)          # the hand-out GptOss.exchange_init relies on
+    assert handles == [b"handles-of-%d" % q for q in range(world)]
     out.put((rank, float(np.abs(y - want).max() / np.abs(want).max()), sorted(deq), (lo, n), r.broadcast_bytes(b"id-from-0" if rank == 0 else None)))
     r.barrier()
     r.close()
