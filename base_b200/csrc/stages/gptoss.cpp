@@ -97,10 +97,10 @@ struct TopkTablesArgs { MoeDims d; TablesManyArgs t; };
 // peer_xchg.cuh: the exchange done by the kernels themselves over peer memory
 constexpr int kPeerMax = 8;
 struct PeerTable { unsigned long long xn_all[kPeerMax], y_recv[kPeerMax], flags[kPeerMax]; int rank, world; };
-struct RowsToPeersArgs { int K, B, tag; float eps; };
-struct RouterPeerArgs { RouterManyArgs r; int tag; };
-struct CombinePeersArgs { int H, top_k, lo, n, B, tag; };
-struct RowsToAPeerArgs { RowsToAArgs r; int tag; };
+struct RowsToPeersArgs { int K, B, tag, layers; float eps; };
+struct RouterPeerArgs { RouterManyArgs r; int tag, layers, per_round; };
+struct CombinePeersArgs { int H, top_k, lo, n, B, tag, layers; };
+struct RowsToAPeerArgs { RowsToAArgs r; int tag, layers; };
 struct RetileSegArgs { int R, K, n_mat; };
 constexpr int kBdThreads = 192, kBdSmemBytes = 6 * (8192 + 16 * 1024) + 64 * 129 * 4 + 512;
 constexpr int kBmThreads = 192, kBmSmemBytes = 8 * (16 * (8 * 128 + 64) + 8 * 8 * 128) + 192 * 8 + 4096;

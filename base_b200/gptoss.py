@@ -161,6 +161,13 @@ class GptOss:
         self.comm_init(ranks.broadcast_bytes(GptOss.new_comm_id() if ranks.rank == 0 else None))
         return "nccl"
 
+    def peer_trace(self) -> np.ndarray:
+        """u64 [layers][8] time stamps (ns) of the last step's exchanging kernels: rows_to_peers start, router start,
+        router after its wait, combine start, the next normalisation's start, after its wait."""
+        out = bytearray(self.cfg.layers * 64)
+        self.base.execute_into(self.art.extras["fetchPeerTrace"], b"", out)
+        return np.frombuffer(bytes(out), dtype="<u8").reshape(self.cfg.layers, 8)
+
     def exchange_close(self, ranks) -> None:
         """Unmap the other ranks' memory and meet them, so that no rank frees a buffer another still maps.  Call on
         every rank before `close()` when `exchange_init` returned "peer" (harmless otherwise)."""

@@ -1,0 +1,51 @@
+"""Run a few decode steps of a gpt-oss-shaped model and print the time per step: the small, fixed command to put under
+a profiler (`ncu -k regex:<kernel> ... python -m base_b200.step_runner --layers 2`) or a launch-ladder, in the role of
+the reference's profile.py (applications/gpt-oss/profile.py:67-82: load once, replay steps, time them).
+
+Weights are generated on the device from the seed, the KV cache is filled with the seeded synthetic rows, so a step at
+`--context` costs what a step after a real prompt of that length costs, without feeding the prompt.
+"""
+from __future__ import annotations
+
+import argparse
+import dataclasses
+import json
+
+import numpy as np
+
+from .gptoss import BATCHED, BLOCK_SCALED, GPT_OSS_20B, PDL, PERSISTENT, GptOss
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--shapes", choices=("20b", "120b"), default="20b", help="32 or 128 experts (hidden 2880 either way)")
+    ap.add_argument("--layers", type=int, default=2)
+    ap.add_argument("--batch", type=int, default=32, help="sequences; 1 with --persistent runs the one-kernel step")
+    ap.add_argument("--context", type=int, default=2048)
+    ap.add_argument("--vocab", type=int, default=GPT_OSS_20B.vocab, help="a small vocabulary keeps a profiled process small")
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--persistent", action="store_true", help="batch 1: the persistent step kernel with block-scaled experts")
+    ap.add_argument("--ladder", action="store_true", help="also print the launch ladder of one step (one GPU, batched step)")
+    a = ap.parse_args()
+    model = dataclasses.replace(GPT_OSS_20B, layers=a.layers, experts=128 if a.shapes == "120b" else 32, vocab=a.vocab)
+    if a.persistent:
+        cfg = dataclasses.replace(model, batch=1, max_seq=a.context + a.steps + 8, flags=PDL | PERSISTENT | BLOCK_SCALED)
+    else:
+        cfg = dataclasses.replace(model, batch=a.batch, max_seq=a.context + a.steps + 8, flags=PDL | BATCHED)
+    m = GptOss(cfg)
+    m.fill_kv()
+    toks = np.random.default_rng(7).integers(0, cfg.vocab, size=cfg.batch)
+    m.prep([int(t) for t in toks], [a.context] * cfg.batch)
+    out, ms = m.decode(a.steps, timed=True)
+    line = {"shapes": a.shapes, "layers": a.layers, "batch": cfg.batch, "context": a.context, "steps": a.steps,
+            "ms_per_step": ms / a.steps, "last_tokens": [int(t) for t in out[-1][:4]]}
+    if a.ladder and not a.persistent:
+        n = m.capture()
+        line["launches_per_step"] = n
+        line["ladder_us"] = [[first, last, round(bucket, 2)] for first, last, _, bucket, _ in m.launch_ladder(range(1, n + 1), reps=5)]
+    print(json.dumps(line))
+    m.close()
+
+
+if __name__ == "__main__":
+    main()

@@ -728,12 +728,12 @@ def run_batched(a, rank: int, world: int, local: int):
                               "dense_tc_gemm_lm_head": {"gbs": cfg.vocab * cfg.hidden * 2 / (lm_ms * 1e-3 / iters) / 1e9, "us_per_launch": lm_ms * 1e3 / iters},
                               "attn_decode_batch": {"us_per_launch": per_launch(at_ms) * 1e6}},
             "whole_step": {"bytes_per_gpu": step_bytes, "achieved": step_bytes / step_s / 1e9, "frac": step_bytes / step_s / 1e9 / peak}}
-    launches_per_step = 1 + cfg.layers * 14 + 3
+    launches_per_step = m.capture()          # counted by the library from the step's own launch sequence
     line = {"metric": metric, "value": value, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup,
             "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "mxfp4 experts / bf16 dense weights, f32 accumulate", "data": "synthetic", "config": config,
             "e2e": {"value": Bg * a.steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 8 * per, "d2h_bytes_per_step": 4 * per},
-            "gpu_launches": a.steps * len(rep_ms) * (launches_per_step + (1 if exchange == "peer" else 0)), "clocks": clocks, "roofline": roof,
+            "gpu_launches": a.steps * len(rep_ms) * launches_per_step, "clocks": clocks, "roofline": roof,
             "repeats": {"n": len(rep_ms), "ms_per_step": [round(r / a.steps, 5) for r in rep_ms], "reported": "median",
                         "min_tokens_per_s": Bg * a.steps / (max(rep_ms) * 1e-3), "max_tokens_per_s": Bg * a.steps / (min(rep_ms) * 1e-3)}}
     m.exchange_close(ranks)

@@ -87,7 +87,7 @@ def test_dense_gemm_accumulator_rows_and_numpy(ctx):
     L, c = ctx
     errs = {}
     for rows16 in (1, 0):
-        out, ref = run_gemm(L, c, 64, 128, 5, 0, rows16, 2, np.random.default_rng(1))
+        out, ref = run_gemm(L, c, 64, 128, 32, 0, rows16, 2, np.random.default_rng(1))   # 32 tokens: all 64 accumulator rows in use
         errs[rows16] = rel(out, ref)
     print("max-rel-err by accumulator row placement:", errs)
     assert errs[1] < 2e-5 and errs[0] > 10 * errs[1]
