@@ -205,11 +205,14 @@ dense_tc_gemm(const uint8_t *__restrict__ Wt, const uint8_t *__restrict__ At, co
   // few rows per CTA (qkv, o-proj): small slots, many of them in flight; many rows (lm_head): 6 slots of 24 KB
   const int Rh = bd_rh(a.B);
   const uint32_t a_bytes = 256u * uint32_t(Rh);                // the A tile of one pass and K chunk
-  const uint32_t slot_bytes = a_bytes + uint32_t(max(1, min(kBdMaxGroups, g_hi - g_lo))) * 1024u;
+  // A ring slot holds TWO consecutive K chunks (the last one of an odd count: one): the hand-over of a slot between
+  // producer, tensor core and back (two mbarrier waits, a commit) costs about 0.25 us whatever the slot holds, and
+  // with one chunk per slot that, not bytes or instructions, was the kernel's time (measured by leaving the A copies
+  // and the instructions out: 17 of 20 us stayed).
+  const uint32_t b_max = uint32_t(max(1, min(kBdMaxGroups, g_hi - g_lo))) * 1024u;
+  const uint32_t slot_bytes = 2u * (a_bytes + b_max);
   const uint32_t n_slots = min(uint32_t(kBdSlots), uint32_t(kBdRingBytes) / slot_bytes);
-  // every CTA reads the same A piece for a given K chunk: start each CTA at a different chunk, so that at any moment
-  // the CTAs ask L2 for different lines (a CTA's own summation order stays fixed)
-  const int c_off = int((blockIdx.x * 7u) % uint32_t(nchunks));
+  const int npairs = (nchunks + 1) >> 1;
 
   if (tid == 0) {
     for (int i = 0; i < kBdSlots; ++i) { mbar_init(&bars->full[i], 1); mbar_init(&bars->empty[i], 1); }
@@ -232,14 +235,18 @@ dense_tc_gemm(const uint8_t *__restrict__ Wt, const uint8_t *__restrict__ At, co
       for (int j = 0; j < jobs; ++j) {
         const int u = j / passes, pass = j % passes;
         const int g0 = g_lo + u * kBdMaxGroups, ng = min(kBdMaxGroups, g_hi - g0);
-        for (int c = 0; c < nchunks; ++c, ++q) {
+        const uint32_t b_bytes = uint32_t(ng) * 1024u;
+        const uint8_t *asrc = At + size_t(pass) * nchunks * a_bytes, *bsrc = Wt + size_t(g0) * 1024;
+        for (int p = 0; p < npairs; ++p, ++q) {
           const uint32_t s = q % n_slots;
           if (q >= n_slots && !bd_wait(&bars->empty[s], ((q / n_slots) - 1) & 1, bars, status, 61)) { j = jobs; break; }
           uint8_t *dst = ring + size_t(s) * slot_bytes;
-          mbar_expect_tx(&bars->full[s], a_bytes + uint32_t(ng) * 1024u);
-          const int cc = (c + c_off) % nchunks;
-          bulk_g2s(dst, At + (size_t(pass) * nchunks + cc) * a_bytes, a_bytes, &bars->full[s]);
-          bulk_g2s(dst + a_bytes, Wt + (size_t(cc) * RG + g0) * 1024, uint32_t(ng) * 1024u, &bars->full[s]);
+          const int c0 = 2 * p;
+          const uint32_t nck = c0 + 1 < nchunks ? 2u : 1u;
+          mbar_expect_tx(&bars->full[s], nck * (a_bytes + b_bytes));
+          bulk_g2s(dst, asrc + size_t(c0) * a_bytes, nck * a_bytes, &bars->full[s]);        // consecutive chunks of A are contiguous
+          bulk_g2s(dst + 2 * a_bytes, bsrc + size_t(c0) * RG * 1024, b_bytes, &bars->full[s]);
+          if (nck == 2) bulk_g2s(dst + 2 * a_bytes + b_bytes, bsrc + size_t(c0 + 1) * RG * 1024, b_bytes, &bars->full[s]);
         }
       }
     }
@@ -255,16 +262,21 @@ dense_tc_gemm(const uint8_t *__restrict__ Wt, const uint8_t *__restrict__ At, co
       tc_fence_after_sync();
       const uint32_t idesc = tc_idesc_bf16(kBdRows, N);
       bool ok = true;
-      for (int c = 0; c < nchunks; ++c, ++q) {
+      const uint32_t b_bytes = uint32_t(ng) * 1024u;
+      for (int p = 0; p < npairs; ++p, ++q) {
         const uint32_t s = q % n_slots;
         ok = bd_wait(&bars->full[s], (q / n_slots) & 1, bars, status, 63);
         if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t sa = smem_u32(ring + size_t(s) * slot_bytes), sb = sa + a_bytes;
-        const uint64_t da = tc_smem_desc(sa, 2 * Rh * 16, 128), db = tc_smem_desc(sb, 128, 1024);
-        bd_mma4_warp(acc, d_step, da, db, idesc, c > 0, uint64_t(4 * Rh));
+        const uint32_t sa = smem_u32(ring + size_t(s) * slot_bytes), sb = sa + 2 * a_bytes;
+        const int nck = 2 * p + 1 < nchunks ? 2 : 1;
+        for (int kk = 0; kk < nck; ++kk) {
+          const uint64_t da = tc_smem_desc(sa + uint32_t(kk) * a_bytes, 2 * Rh * 16, 128);
+          const uint64_t db = tc_smem_desc(sb + uint32_t(kk) * b_bytes, 128, 1024);
+          bd_mma4_warp(acc, d_step, da, db, idesc, p > 0 || kk > 0, uint64_t(4 * Rh));
+        }
         tc_commit_warp(&bars->empty[s], true);
-        tc_commit_warp(&bars->done[j & 1], c == nchunks - 1);
+        tc_commit_warp(&bars->done[j & 1], p == npairs - 1);
         __syncwarp();
       }
       if (!ok) break;

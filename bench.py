@@ -455,7 +455,7 @@ def run_batch1(a, rank: int, world: int, local: int, ranks=None, emit: bool = Tr
     from base_b200.gptoss import GPT_OSS_20B, GptOss, PDL, PERSISTENT, BLOCK_SCALED
     import dataclasses
     mx = a.step == "persistent" and a.experts == "block-scaled"
-    cfg = dataclasses.replace(GPT_OSS_20B, max_seq=a.prompt + a.warmup + (max(1, a.repeats) + 1) * a.steps + 8,
+    cfg = dataclasses.replace(GPT_OSS_20B, max_seq=a.prompt + a.warmup + 2 * a.steps + 8,
                               flags=PDL | (PERSISTENT if a.step == "persistent" else 0) | (BLOCK_SCALED if mx else 0))
     if a.layers:
         cfg = dataclasses.replace(cfg, layers=a.layers)
@@ -519,8 +519,9 @@ def run_batch1(a, rank: int, world: int, local: int, ranks=None, emit: bool = Tr
     sampler = ClockSampler(local)
     sampler.start()
     sampler.mark()
-    # the K-step loop, `repeats` times back to back (each continues where the last one stopped); every repeat
-    # is timed by device events and reduced to the max over ranks; the line reports the median repeat
+    # the K-step loop, `repeats` times: every repeat generates the SAME K positions after the prompt (the KV rows it
+    # wrote are overwritten by the next), so the repeats are the same work; each is timed by device events and
+    # reduced to the max over ranks; the line reports the median repeat
     rep_ms = []
     for _ in range(max(1, a.repeats)):
         barrier()
@@ -528,15 +529,14 @@ def run_batch1(a, rank: int, world: int, local: int, ranks=None, emit: bool = Tr
         toks, ms_r = m.decode(a.steps, timed=True)
         barrier()
         rep_ms.append(max_over_ranks(ms_r))
-        tok, pos = int(toks[-1, 0]), pos + a.steps
     order = sorted(range(len(rep_ms)), key=lambda i: rep_ms[i])
     mid = order[len(order) // 2]
     ms = rep_ms[mid]
-    pos_mid = pos - (len(rep_ms) - mid) * a.steps       # where the median repeat started
+    pos_mid = pos
     value = world * a.steps / (ms * 1e-3)
 
     # end to end: one execute_into per token, host buffers in and out
-    # continues from where the device loop stopped
+    # the same K positions once more
     tok2, pos2 = tok, pos
     barrier()
     t0 = time.perf_counter()
@@ -619,7 +619,7 @@ def run_batched(a, rank: int, world: int, local: int):
     reps = max(1, a.repeats)
     if a.layers:
         model = dataclasses.replace(model, layers=a.layers)
-    cfg = dataclasses.replace(model, batch=per, max_seq=a.prompt + a.warmup + (reps + 1) * a.steps + 8,
+    cfg = dataclasses.replace(model, batch=per, max_seq=a.prompt + a.warmup + 2 * a.steps + 8,
                               flags=PDL | BATCHED, ep_rank=rank, ep_world=world)
     metric = METRIC.replace("gpt-oss-20b", name)
     config = {"workload": f"{name} decode, {Bg} sequences, {a.prompt}-token " +
@@ -685,12 +685,11 @@ def run_batched(a, rank: int, world: int, local: int):
         m.prep(toks, [pos] * per)
         out, ms_r = m.decode(a.steps, timed=True)
         barrier()
-        rep_ms.append(max_over_ranks(ms_r))
-        toks, pos = [int(t) for t in out[-1]], pos + a.steps
+        rep_ms.append(max_over_ranks(ms_r))      # every repeat: the same K positions after the prompt
     order = sorted(range(len(rep_ms)), key=lambda i: rep_ms[i])
     mid = order[len(order) // 2]
     ms = rep_ms[mid]
-    pos_mid = pos - (len(rep_ms) - mid) * a.steps
+    pos_mid = pos
     value = Bg * a.steps / (ms * 1e-3)
 
     # end to end: one execute_into per step with host buffers (tokens and positions in, next tokens out)
