@@ -240,7 +240,7 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = bars->tmem_base;
-  // columns: the tokens' scales of two units in flight [0, 192), the weights' scales per ring slot [192, 232), two accumulators [256, 512)
+  // columns: the tokens' scales of two units in flight [0, 192), the weights' scales per ring slot (16 columns each) [192, 256), two accumulators [256, 512)
   const uint32_t tSFA = tmem, tSFB = tmem + 192, tD = tmem + 256;
   pdl_wait();
   pdl_launch_dependents();
@@ -273,8 +273,11 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
   }
   __syncthreads();
   const size_t mbytes = seg16_matrix_bytes(kblocks, G);
-  const uint32_t a_bytes = uint32_t(max(bars->max_nt, 1)) * (kBmKc * 128), slot_bytes = a_bytes + kBmBBytes;
-  const uint32_t n_slots = min(uint32_t(kBmSlots), uint32_t(kBmRingBytes) / slot_bytes);
+  // a ring slot holds TWO consecutive chunks ([digits 0][digits 1][piece 0][piece 1]): handing a slot from the producer to
+  // the tensor core and back costs about as much as streaming half a chunk, so it is paid once per two
+  const uint32_t a_bytes = uint32_t(max(bars->max_nt, 1)) * (kBmKc * 128), slot_bytes = 2u * (a_bytes + kBmBBytes);
+  const uint32_t n_slots = min(4u, uint32_t(kBmRingBytes) / slot_bytes);       // 3 or 4: each owns 16 of the 64 scale columns
+  const int npair = (nch + 1) >> 1;
 
   if (warp == 5) {
     // ---- producer
@@ -284,15 +287,21 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
         const BmUnit u = units[ui];
         const int off = offset[u.e] + u.pass * kBmTok, nt = min(kBmTok, count[u.e] - u.pass * kBmTok);
         const uint8_t *wexp = W + size_t(u.e - a.lo) * mbytes;
-        for (int c = 0; c < nch; ++c, ++q) {
+        for (int p = 0; p < npair; ++p, ++q) {
           const uint32_t s = q % n_slots;
           if (q >= n_slots && !bm_wait(&bars->empty[s], ((q / n_slots) - 1) & 1, bars, status, 72)) { ui = n_units; break; }
-          const int kcc = min(kBmKc, kblocks - c * kBmKc);
-          const uint32_t bbytes = uint32_t(seg16_bytes(kcc, u.ng));
+          const int c0 = 2 * p, nck = c0 + 1 < nch ? 2 : 1;
+          const int kc0 = min(kBmKc, kblocks - c0 * kBmKc), kc1 = nck == 2 ? min(kBmKc, kblocks - (c0 + 1) * kBmKc) : 0;
+          const uint32_t bb0 = uint32_t(seg16_bytes(kc0, u.ng)), bb1 = nck == 2 ? uint32_t(seg16_bytes(kc1, u.ng)) : 0u;
+          const uint32_t ab = uint32_t(nt * kBmKc * 128);
           uint8_t *dst = ring + size_t(s) * slot_bytes;
-          mbar_expect_tx(&bars->full[s], bbytes + uint32_t(nt * kBmKc * 128));
-          bulk_g2s(dst + a_bytes, wexp + seg16_offset(c, u.g0 / kBmGroups, kcc, G), bbytes, &bars->full[s]);
-          bulk_g2s(dst, dig + (size_t(c) * a.P + off) * (kBmKc * 128), uint32_t(nt * kBmKc * 128), &bars->full[s]);
+          mbar_expect_tx(&bars->full[s], bb0 + bb1 + uint32_t(nck) * ab);
+          bulk_g2s(dst + 2 * a_bytes, wexp + seg16_offset(c0, u.g0 / kBmGroups, kc0, G), bb0, &bars->full[s]);
+          bulk_g2s(dst, dig + (size_t(c0) * a.P + off) * (kBmKc * 128), ab, &bars->full[s]);
+          if (nck == 2) {
+            bulk_g2s(dst + 2 * a_bytes + kBmBBytes, wexp + seg16_offset(c0 + 1, u.g0 / kBmGroups, kc1, G), bb1, &bars->full[s]);
+            bulk_g2s(dst + a_bytes, dig + (size_t(c0 + 1) * a.P + off) * (kBmKc * 128), ab, &bars->full[s]);
+          }
         }
       }
     }
@@ -307,23 +316,28 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
       tc_fence_after_sync();
       const uint32_t id0 = mx_idesc(128, N, 0, 0), id2 = mx_idesc(128, N, 2, 2);
       bool ok = true;
-      for (int c = 0; c < nch && ok; ++c, ++q) {
+      for (int p = 0; p < npair && ok; ++p, ++q) {
         const uint32_t s = q % n_slots;
         ok = bm_wait(&bars->full[s], (q / n_slots) & 1, bars, status, 75);
         if (!ok) break;
         tc_fence_after_sync();
-        const int kcc = min(kBmKc, kblocks - c * kBmKc);
-        const uint32_t sa = smem_u32(ring + size_t(s) * slot_bytes), sb = sa + a_bytes, ssf = sb + uint32_t(u.ng * kcc * 128);
-        for (int pp = 0; 4 * pp < kcc; ++pp) {
-          // A in the slot: [token][K block of the chunk][8 digit rows x 16 B]: K blocks 128 B apart, tokens 1 KB apart
-          // B in the slot: [group][K block][8 rows x 16 B]: K blocks 128 B apart, groups kcc x 128 B apart
-          const uint64_t da = tc_smem_desc(sa + uint32_t(4 * pp) * 128, 128, kBmKc * 128);
-          const uint64_t db = tc_smem_desc(sb + uint32_t(4 * pp) * 128, 128, uint32_t(kcc * 128));
-          bm_mma_pair_warp(tDu, da, db, id0, id2, tSFAu + 4 * uint32_t(c * (kBmKc >> 2) + pp), tSFB + s * 8 + uint32_t(pp) * 4,
-                           !(c == 0 && pp == 0), 4 * pp + 2 < kcc, 256u >> 4, 256u >> 4, tc_smem_desc(ssf + uint32_t(pp) * 512, 16, 128));
+        const uint32_t base = smem_u32(ring + size_t(s) * slot_bytes);
+        for (int kk = 0; kk < 2 && 2 * p + kk < nch; ++kk) {
+          const int c = 2 * p + kk, kcc = min(kBmKc, kblocks - c * kBmKc);
+          const uint32_t sa = base + uint32_t(kk) * a_bytes, sb = base + 2 * a_bytes + uint32_t(kk) * kBmBBytes;
+          const uint32_t ssf = sb + uint32_t(u.ng * kcc * 128);
+          for (int pp = 0; 4 * pp < kcc; ++pp) {
+            // A in the slot: [token][K block of the chunk][8 digit rows x 16 B]: K blocks 128 B apart, tokens 1 KB apart
+            // B in the slot: [group][K block][8 rows x 16 B]: K blocks 128 B apart, groups kcc x 128 B apart
+            const uint64_t da = tc_smem_desc(sa + uint32_t(4 * pp) * 128, 128, kBmKc * 128);
+            const uint64_t db = tc_smem_desc(sb + uint32_t(4 * pp) * 128, 128, uint32_t(kcc * 128));
+            bm_mma_pair_warp(tDu, da, db, id0, id2, tSFAu + 4 * uint32_t(c * (kBmKc >> 2) + pp),
+                             tSFB + s * 16 + uint32_t(kk) * 8 + uint32_t(pp) * 4, !(c == 0 && pp == 0), 4 * pp + 2 < kcc, 256u >> 4,
+                             256u >> 4, tc_smem_desc(ssf + uint32_t(pp) * 512, 16, 128));
+          }
         }
         tc_commit_warp(&bars->empty[s], true);
-        tc_commit_warp(&bars->done[ui & 1], c == nch - 1);
+        tc_commit_warp(&bars->done[ui & 1], p == npair - 1);
         __syncwarp();
       }
       if (!ok) break;
