@@ -205,14 +205,17 @@ dense_tc_gemm(const uint8_t *__restrict__ Wt, const uint8_t *__restrict__ At, co
   // few rows per CTA (qkv, o-proj): small slots, many of them in flight; many rows (lm_head): 6 slots of 24 KB
   const int Rh = bd_rh(a.B);
   const uint32_t a_bytes = 256u * uint32_t(Rh);                // the A tile of one pass and K chunk
-  // A ring slot holds TWO consecutive K chunks (the last one of an odd count: one): the hand-over of a slot between
+  // A ring slot holds kc >= 2 consecutive K chunks (the last slot what is left): the hand-over of a slot between
   // producer, tensor core and back (two mbarrier waits, a commit) costs about 0.25 us whatever the slot holds, and
   // with one chunk per slot that, not bytes or instructions, was the kernel's time (measured by leaving the A copies
   // and the instructions out: 17 of 20 us stayed).
+  // kc = 2 chunks per slot, or 3 / 4 where four such slots still fit the ring (few tokens, few rows per CTA).
   const uint32_t b_max = uint32_t(max(1, min(kBdMaxGroups, g_hi - g_lo))) * 1024u;
-  const uint32_t slot_bytes = 2u * (a_bytes + b_max);
+  int kc = 2;
+  while (kc < 4 && uint32_t(kc + 1) * (a_bytes + b_max) * 4u <= uint32_t(kBdRingBytes)) ++kc;
+  const uint32_t slot_bytes = uint32_t(kc) * (a_bytes + b_max);
   const uint32_t n_slots = min(uint32_t(kBdSlots), uint32_t(kBdRingBytes) / slot_bytes);
-  const int npairs = (nchunks + 1) >> 1;
+  const int npairs = (nchunks + kc - 1) / kc;
 
   if (tid == 0) {
     for (int i = 0; i < kBdSlots; ++i) { mbar_init(&bars->full[i], 1); mbar_init(&bars->empty[i], 1); }
@@ -241,12 +244,12 @@ dense_tc_gemm(const uint8_t *__restrict__ Wt, const uint8_t *__restrict__ At, co
           const uint32_t s = q % n_slots;
           if (q >= n_slots && !bd_wait(&bars->empty[s], ((q / n_slots) - 1) & 1, bars, status, 61)) { j = jobs; break; }
           uint8_t *dst = ring + size_t(s) * slot_bytes;
-          const int c0 = 2 * p;
-          const uint32_t nck = c0 + 1 < nchunks ? 2u : 1u;
+          const int c0 = kc * p;
+          const uint32_t nck = uint32_t(min(kc, nchunks - c0));
           mbar_expect_tx(&bars->full[s], nck * (a_bytes + b_bytes));
           bulk_g2s(dst, asrc + size_t(c0) * a_bytes, nck * a_bytes, &bars->full[s]);        // consecutive chunks of A are contiguous
-          bulk_g2s(dst + 2 * a_bytes, bsrc + size_t(c0) * RG * 1024, b_bytes, &bars->full[s]);
-          if (nck == 2) bulk_g2s(dst + 2 * a_bytes + b_bytes, bsrc + size_t(c0 + 1) * RG * 1024, b_bytes, &bars->full[s]);
+          for (uint32_t kk = 0; kk < nck; ++kk)
+            bulk_g2s(dst + uint32_t(kc) * a_bytes + kk * b_bytes, bsrc + size_t(c0 + int(kk)) * RG * 1024, b_bytes, &bars->full[s]);
         }
       }
     }
@@ -268,8 +271,8 @@ dense_tc_gemm(const uint8_t *__restrict__ Wt, const uint8_t *__restrict__ At, co
         ok = bd_wait(&bars->full[s], (q / n_slots) & 1, bars, status, 63);
         if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t sa = smem_u32(ring + size_t(s) * slot_bytes), sb = sa + 2 * a_bytes;
-        const int nck = 2 * p + 1 < nchunks ? 2 : 1;
+        const uint32_t sa = smem_u32(ring + size_t(s) * slot_bytes), sb = sa + uint32_t(kc) * a_bytes;
+        const int nck = min(kc, nchunks - kc * p);
         for (int kk = 0; kk < nck; ++kk) {
           const uint64_t da = tc_smem_desc(sa + uint32_t(kk) * a_bytes, 2 * Rh * 16, 128);
           const uint64_t db = tc_smem_desc(sb + uint32_t(kk) * b_bytes, 128, 1024);
