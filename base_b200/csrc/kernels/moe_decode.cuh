@@ -81,8 +81,9 @@ moe_router_logits(const float *__restrict__ Wr, const float *__restrict__ br,
 // ---- top-k + softmax over the selected logits -----------------------------------
 // One warp per token.  E <= 128 (4 logits per lane).  Selection is by
 // (logit descending, expert id ascending); NaN logits sort last.
+// idx_copy (optional): a second place for the indices (shared memory of a fused caller).
 B200_DEVICE void topk_softmax_token(const float *__restrict__ logits, int *__restrict__ topk_idx,
-                                    float *__restrict__ topk_w, const MoeDims &d, int t, int lane) {
+                                    float *__restrict__ topk_w, const MoeDims &d, int t, int lane, int *idx_copy = nullptr) {
   float v[4];
   bool taken[4];
 #pragma unroll
@@ -120,6 +121,7 @@ B200_DEVICE void topk_softmax_token(const float *__restrict__ logits, int *__res
     for (int j = 0; j < d.top_k && j < 8; ++j) { ex[j] = __expf(sel_v[j] - m); s += ex[j]; }
     for (int j = 0; j < d.top_k && j < 8; ++j) {
       topk_idx[size_t(t) * d.top_k + j] = sel_e[j];
+      if (idx_copy) idx_copy[t * d.top_k + j] = sel_e[j];
       topk_w[size_t(t) * d.top_k + j] = ex[j] / s;
     }
   }

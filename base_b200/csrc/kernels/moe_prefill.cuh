@@ -381,19 +381,65 @@ moe_route_tables_many(const int *__restrict__ topk_idx, int *__restrict__ route,
   route_tables_many_body(topk_idx, route, tiles, a);
 }
 
-// Top-k + softmax (moe_topk_softmax, one warp per token) and the routing tables in ONE CTA of 1024 threads: the batched
-// decode step's form (a launch less per layer).  T = A / top_k tokens.
-struct TopkTablesArgs { MoeDims d; TablesManyArgs t; };
+// Top-k + softmax (one warp per token, as moe_topk_softmax) and the routing tables (count / offset / active / perm, as
+// moe_route_tables_many, without the token-tile list) in ONE CTA of 1024 threads, for the batched decode step:
+// A = T * top_k <= kTtMaxA assignments.  The indices stay in shared memory; a warp per expert counts its assignments
+// with ballots over 32 at a time, warp 0 scans the counts, the warps walk their experts once more and write the
+// permutation (stable in the assignment index by construction): no atomics, no per-warp histograms.
+constexpr int kTtMaxA = 4096;
+struct TopkTablesArgs { MoeDims d; TablesManyArgs t; int do_topk; };   // do_topk = 0: topk_idx was written by moe_topk_softmax (many tokens: a warp each, in parallel)
 
 extern "C" __global__ void __launch_bounds__(1024)
 moe_topk_tables_many(const float *__restrict__ logits, int *__restrict__ topk_idx, float *__restrict__ topk_w,
-                     int *__restrict__ route, int *__restrict__ tiles, TopkTablesArgs a) {
+                     int *__restrict__ route, TopkTablesArgs a) {
   pdl_wait();
   pdl_launch_dependents();
-  const int T = a.t.A / a.d.top_k;
-  for (int t = threadIdx.x >> 5; t < T; t += 32) topk_softmax_token(logits, topk_idx, topk_w, a.d, t, threadIdx.x & 31);
-  __syncthreads();                           // the tables below read topk_idx written by this CTA
-  route_tables_many_body(topk_idx, route, tiles, a.t);
+  __shared__ int s_idx[kTtMaxA];
+  __shared__ int s_count[128], s_offset[129];
+  const int A = a.t.A, E = a.t.E, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int T = A / a.d.top_k;
+  int *n_active = route, *count = route + 1, *offset = route + 1 + E, *active = offset + E + 1, *perm = active + E;
+  if (a.do_topk) {
+    for (int t = warp; t < T; t += 32) topk_softmax_token(logits, topk_idx, topk_w, a.d, t, lane, s_idx);
+  } else {
+    for (int i = tid; i < A; i += 1024) s_idx[i] = __ldcg(topk_idx + i);
+  }
+  __syncthreads();
+  for (int e = warp; e < E; e += 32) {
+    int n = 0;
+    for (int base = 0; base < A; base += 32) n += __popc(__ballot_sync(0xffffffffu, base + lane < A && s_idx[base + lane] == e));
+    if (lane == 0) s_count[e] = n;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int run = 0, na = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + lane, c = e < E ? s_count[e] : 0;
+      int inc = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += v;
+      }
+      if (e < E) { s_offset[e] = run + inc - c; offset[e] = run + inc - c; count[e] = c; }
+      const unsigned act = __ballot_sync(0xffffffffu, c > 0);
+      if (c > 0) active[na + __popc(act & ((1u << lane) - 1u))] = e;
+      na += __popc(act);
+      run += __shfl_sync(0xffffffffu, inc, 31);
+    }
+    if (lane == 0) { s_offset[E] = run; offset[E] = run; *n_active = na; }
+    for (int i = na + lane; i < E; i += 32) active[i] = -1;
+  }
+  __syncthreads();
+  for (int e = warp; e < E; e += 32) {
+    int at = s_offset[e];
+    for (int base = 0; base < A; base += 32) {
+      const bool mine = base + lane < A && s_idx[base + lane] == e;
+      const unsigned m = __ballot_sync(0xffffffffu, mine);
+      if (mine) perm[at + __popc(m & ((1u << lane) - 1u))] = base + lane;
+      at += __popc(m);
+    }
+  }
 }
 
 // f32 rows -> bf16 (round to nearest even), 8 elements per thread.

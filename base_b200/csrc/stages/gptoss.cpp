@@ -93,7 +93,7 @@ struct BatchMxArgs { MoeDims d; int lo, n, P; };
 struct RouterManyArgs { int T, H, E; };
 struct TablesManyArgs { int A, E, lo, n; };
 struct CombineRangeArgs { int H, top_k, lo, n; };
-struct TopkTablesArgs { MoeDims d; TablesManyArgs t; };
+struct TopkTablesArgs { MoeDims d; TablesManyArgs t; int do_topk; };
 // peer_xchg.cuh: the exchange done by the kernels themselves over peer memory
 constexpr int kPeerMax = 8;
 struct PeerTable { unsigned long long xn_all[kPeerMax], y_recv[kPeerMax], flags[kPeerMax]; int rank, world; };
