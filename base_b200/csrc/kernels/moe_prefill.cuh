@@ -270,21 +270,24 @@ moe_prefill_down(const uint4 *__restrict__ tcodes, const uint32_t *__restrict__ 
 // divided among grid.y CTAs: many-token callers use grid.y = 1, the batched decode step grid.y = E / 8)
 struct RouterManyArgs { int T, H, E; };
 
-B200_DEVICE void router_many_body(const float *__restrict__ Wr, const float *__restrict__ br, const float *__restrict__ x,
-                                  float *__restrict__ logits, const RouterManyArgs &a) {
+template <int NT>
+B200_DEVICE void router_many_tokens(const float *__restrict__ Wr, const float *__restrict__ br, const float *__restrict__ x,
+                                    float *__restrict__ logits, const RouterManyArgs &a) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int t0 = blockIdx.x * 4, nt = min(4, a.T - t0), n4 = a.H >> 2;
-  float4 *xs = reinterpret_cast<float4 *>(dyn_smem);            // [4][H]
+  const int t0 = blockIdx.x * NT, nt = min(NT, a.T - t0), n4 = a.H >> 2;
+  float4 *xs = reinterpret_cast<float4 *>(dyn_smem);            // [NT][H]
   // x may have been written by another GPU while this kernel waited: read it through L2, not the read-only path
   for (int i = tid; i < nt * n4; i += 256) xs[i] = __ldcg(reinterpret_cast<const float4 *>(x + size_t(t0) * a.H) + i);
   __syncthreads();
   for (int e = warp + 8 * blockIdx.y; e < a.E; e += 8 * gridDim.y) {      // grid.y CTAs share the experts
     const float4 *w4 = reinterpret_cast<const float4 *>(Wr + size_t(e) * a.H);
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc[NT];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) acc[i] = 0.f;
     for (int c = lane; c < n4; c += 32) {
       const float4 w = __ldg(w4 + c);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < NT; ++i) {
         if (i < nt) {
           const float4 xv = xs[i * n4 + c];
           acc[i] = fmaf(w.x, xv.x, acc[i]); acc[i] = fmaf(w.y, xv.y, acc[i]);
@@ -292,13 +295,23 @@ B200_DEVICE void router_many_body(const float *__restrict__ Wr, const float *__r
         }
       }
     }
+    float mine = 0.f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) acc[i] = warp_sum(acc[i]);
-    if (lane < nt) {
-      const float v = lane == 0 ? acc[0] : lane == 1 ? acc[1] : lane == 2 ? acc[2] : acc[3];
-      logits[size_t(t0 + lane) * a.E + e] = v + br[e];
+    for (int i = 0; i < NT; ++i) {
+      const float v = warp_sum(acc[i]);
+      if (lane == i) mine = v;
     }
+    if (lane < nt) logits[size_t(t0 + lane) * a.E + e] = mine + br[e];
   }
+}
+
+// Tokens per CTA: 4 (dynamic shared memory 4 * H * 4 bytes, grid.x = ceil(T / 4)), or 8 when the launch has grid.x =
+// ceil(T / 8) (8 * H * 4 bytes): with hundreds of tokens the CTAs then read half as many bytes from L2 for the same
+// dot products (same fold per token and expert, same logits).
+B200_DEVICE void router_many_body(const float *__restrict__ Wr, const float *__restrict__ br, const float *__restrict__ x,
+                                  float *__restrict__ logits, const RouterManyArgs &a) {
+  if (a.T > 4 * int(gridDim.x)) router_many_tokens<8>(Wr, br, x, logits, a);
+  else router_many_tokens<4>(Wr, br, x, logits, a);
 }
 
 extern "C" __global__ void __launch_bounds__(256)
@@ -383,9 +396,9 @@ moe_route_tables_many(const int *__restrict__ topk_idx, int *__restrict__ route,
 
 // Top-k + softmax (one warp per token, as moe_topk_softmax) and the routing tables (count / offset / active / perm, as
 // moe_route_tables_many, without the token-tile list) in ONE CTA of 1024 threads, for the batched decode step:
-// A = T * top_k <= kTtMaxA assignments.  The indices stay in shared memory; a warp per expert counts its assignments
-// with ballots over 32 at a time, warp 0 scans the counts, the warps walk their experts once more and write the
-// permutation (stable in the assignment index by construction): no atomics, no per-warp histograms.
+// A = T * top_k <= kTtMaxA assignments.  The indices stay in shared memory; counts by shared-memory atomics (integers:
+// order-free), warp 0 scans them, then a warp per expert walks the assignments 32 at a time with ballots and writes the
+// permutation (stable in the assignment index by construction, no per-warp histograms).
 constexpr int kTtMaxA = 4096;
 struct TopkTablesArgs { MoeDims d; TablesManyArgs t; int do_topk; };   // do_topk = 0: topk_idx was written by moe_topk_softmax (many tokens: a warp each, in parallel)
 
@@ -404,12 +417,9 @@ moe_topk_tables_many(const float *__restrict__ logits, int *__restrict__ topk_id
   } else {
     for (int i = tid; i < A; i += 1024) s_idx[i] = __ldcg(topk_idx + i);
   }
+  if (tid < 128) s_count[tid] = 0;
   __syncthreads();
-  for (int e = warp; e < E; e += 32) {
-    int n = 0;
-    for (int base = 0; base < A; base += 32) n += __popc(__ballot_sync(0xffffffffu, base + lane < A && s_idx[base + lane] == e));
-    if (lane == 0) s_count[e] = n;
-  }
+  for (int i = tid; i < A; i += 1024) atomicAdd(&s_count[s_idx[i]], 1);          // integer counts: order-free
   __syncthreads();
   if (warp == 0) {
     int run = 0, na = 0;
