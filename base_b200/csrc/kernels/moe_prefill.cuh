@@ -270,7 +270,10 @@ moe_prefill_down(const uint4 *__restrict__ tcodes, const uint32_t *__restrict__ 
 // divided among grid.y CTAs: many-token callers use grid.y = 1, the batched decode step grid.y = E / 8)
 struct RouterManyArgs { int T, H, E; };
 
-template <int NT>
+// NT tokens per CTA, EW experts per warp at a time.  Every (token, expert) pair walks the token's row in shared memory and
+// the expert's row in L2: EW experts share one read of the token's row, NT tokens one read of the expert's row.  The
+// per-lane sums and the fold of a pair are the same for any NT and EW, so the logits do not depend on them.
+template <int NT, int EW>
 B200_DEVICE void router_many_tokens(const float *__restrict__ Wr, const float *__restrict__ br, const float *__restrict__ x,
                                     float *__restrict__ logits, const RouterManyArgs &a) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -279,39 +282,59 @@ B200_DEVICE void router_many_tokens(const float *__restrict__ Wr, const float *_
   // x may have been written by another GPU while this kernel waited: read it through L2, not the read-only path
   for (int i = tid; i < nt * n4; i += 256) xs[i] = __ldcg(reinterpret_cast<const float4 *>(x + size_t(t0) * a.H) + i);
   __syncthreads();
-  for (int e = warp + 8 * blockIdx.y; e < a.E; e += 8 * gridDim.y) {      // grid.y CTAs share the experts
-    const float4 *w4 = reinterpret_cast<const float4 *>(Wr + size_t(e) * a.H);
-    float acc[NT];
+  const int stride = 8 * gridDim.y;                             // grid.y CTAs share the experts
+  for (int e0 = warp + 8 * blockIdx.y; e0 < a.E; e0 += stride * EW) {
+    const float4 *w4[EW];
 #pragma unroll
-    for (int i = 0; i < NT; ++i) acc[i] = 0.f;
+    for (int j = 0; j < EW; ++j) w4[j] = reinterpret_cast<const float4 *>(Wr + size_t(min(e0 + j * stride, a.E - 1)) * a.H);
+    float acc[EW][NT];
+#pragma unroll
+    for (int j = 0; j < EW; ++j)
+#pragma unroll
+      for (int i = 0; i < NT; ++i) acc[j][i] = 0.f;
     for (int c = lane; c < n4; c += 32) {
-      const float4 w = __ldg(w4 + c);
+      float4 w[EW];
+#pragma unroll
+      for (int j = 0; j < EW; ++j) w[j] = __ldg(w4[j] + c);
 #pragma unroll
       for (int i = 0; i < NT; ++i) {
         if (i < nt) {
           const float4 xv = xs[i * n4 + c];
-          acc[i] = fmaf(w.x, xv.x, acc[i]); acc[i] = fmaf(w.y, xv.y, acc[i]);
-          acc[i] = fmaf(w.z, xv.z, acc[i]); acc[i] = fmaf(w.w, xv.w, acc[i]);
+#pragma unroll
+          for (int j = 0; j < EW; ++j) {
+            acc[j][i] = fmaf(w[j].x, xv.x, acc[j][i]); acc[j][i] = fmaf(w[j].y, xv.y, acc[j][i]);
+            acc[j][i] = fmaf(w[j].z, xv.z, acc[j][i]); acc[j][i] = fmaf(w[j].w, xv.w, acc[j][i]);
+          }
         }
       }
     }
-    float mine = 0.f;
 #pragma unroll
-    for (int i = 0; i < NT; ++i) {
-      const float v = warp_sum(acc[i]);
-      if (lane == i) mine = v;
+    for (int j = 0; j < EW; ++j) {
+      const int e = e0 + j * stride;
+      float mine = 0.f;
+#pragma unroll
+      for (int i = 0; i < NT; ++i) {
+        const float v = warp_sum(acc[j][i]);
+        if (lane == i) mine = v;
+      }
+      if (lane < nt && e < a.E) logits[size_t(t0 + lane) * a.E + e] = mine + br[e];
     }
-    if (lane < nt) logits[size_t(t0 + lane) * a.E + e] = mine + br[e];
   }
 }
 
-// Tokens per CTA: 4 (dynamic shared memory 4 * H * 4 bytes, grid.x = ceil(T / 4)), or 8 when the launch has grid.x =
-// ceil(T / 8) (8 * H * 4 bytes): with hundreds of tokens the CTAs then read half as many bytes from L2 for the same
-// dot products (same fold per token and expert, same logits).
+// The launch picks the form: grid.x = ceil(T / 8) (and 8 * H * 4 bytes of dynamic shared memory) means 8 tokens per CTA,
+// else 4 (4 * H * 4 bytes); a warp with several experts to do (E / (8 x grid.y)) takes 4 (2 with 8 tokens) at a time.
 B200_DEVICE void router_many_body(const float *__restrict__ Wr, const float *__restrict__ br, const float *__restrict__ x,
                                   float *__restrict__ logits, const RouterManyArgs &a) {
-  if (a.T > 4 * int(gridDim.x)) router_many_tokens<8>(Wr, br, x, logits, a);
-  else router_many_tokens<4>(Wr, br, x, logits, a);
+  const int per_warp = a.E / (8 * int(gridDim.y));
+  if (a.T > 4 * int(gridDim.x)) {
+    if (per_warp >= 2) router_many_tokens<8, 2>(Wr, br, x, logits, a);
+    else router_many_tokens<8, 1>(Wr, br, x, logits, a);
+  } else if (per_warp >= 4) {
+    router_many_tokens<4, 4>(Wr, br, x, logits, a);
+  } else {
+    router_many_tokens<4, 1>(Wr, br, x, logits, a);
+  }
 }
 
 extern "C" __global__ void __launch_bounds__(256)
