@@ -1,31 +1,34 @@
 #!/usr/bin/env python3
 """Headline benchmark: gpt-oss-20b-architecture MXFP4 greedy decode, tokens/s.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
-                    [--step persistent|per-op] [--experts block-scaled|cuda-core]
-                    [--workload gptoss|qwen2|prefill]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--batch B] [--repeats R]
+                    [--workload gptoss|gptoss120b|qwen2|prefill] [--exchange peer|nccl]
+                    [--step persistent|per-op] [--experts block-scaled|cuda-core] [--layers L] [--synthetic-kv]
 
-Default workload (BASELINE config 3, batch 1): 24 layers, hidden 2880, 64 q / 8 kv
-heads of 64, sliding window 128 alternating with full attention, sinks, 32 MXFP4
-experts top-4, vocab 201088; random-init weights generated on the device from a
-seed; a 2048-token random prompt is fed token by token (as the reference feeds
-prompts, lean/algorithms/Qwen2Common.lean:1446-1457), then K greedy tokens are
-timed.  A step = one decode step of every sequence; by default it is ONE
-persistent cooperative kernel whose expert phases run on the block-scaled tensor
-cores (tcgen05.mma kind::mxf4; --experts cuda-core selects the CUDA-core expert
-phases), with --step per-op a CUDA graph of one launch per operation.
+Default workload (BASELINE config 3 at batch 32): 24 layers, hidden 2880, 64 q / 8 kv heads of 64, sliding window 128
+alternating with full attention, sinks, 32 MXFP4 experts top-4, vocab 201088; random-init weights generated on the
+device from a seed; 32 sequences with 2048-token random prompts fed token by token (as the reference feeds prompts,
+lean/algorithms/Qwen2Common.lean:1446-1457), then K greedy tokens per sequence are timed.  A step = one decode step of
+every sequence = one CUDA graph of the batched kernels (dense layers and MXFP4 experts on the tcgen05 tensor cores).
 
-value   tokens/s with the argmax fed back on the device (stage `decode`), timed
-        with CUDA events on the launching stream.
-e2e     the same metric through Base.execute_into(`infer`) once per token with
-        host buffers: 8 bytes in, 4 bytes out per sequence, wall clock.
-N > 1   one process per GPU (torchrun), every rank decodes its own sequence on a
-        full replica (no data-path collective), so scaling is weak; the value
-        is the sum over ranks over the slowest rank's time.
+value   tokens/s with the argmax fed back on the device (stage `decode`), timed with CUDA events on the launching
+        stream; the K-step loop runs R times over the same K positions, the line reports the median repeat.
+e2e     the same metric through Base.execute_into(`infer`) once per step with host buffers: 8 bytes in, 4 bytes out
+        per sequence, wall clock.
+N > 1   one process per GPU (torchrun), ONE model sharded over the N GPUs: every rank holds B / N sequences (their KV
+        caches, attention data parallel) and E / N experts; per layer the normalised rows go to every rank and the
+        experts' partial sums back to the sequences' owners, as NVLink stores from the producing kernels (--exchange
+        peer) or as NCCL all-gather + all-to-all inside the graph (--exchange nccl).  The work is fixed as N grows
+        ("scaling": "strong"); value = all sequences' tokens over the slowest rank's time.
+batch1  at N = 1 the line also carries BASELINE config 3 at batch 1 on the same GPU (`"batch1"`: the persistent
+        cooperative kernel, with its own value, e2e, roofline and phase stamps); `--batch 1` runs only that (a replica
+        per GPU under torchrun; --step / --experts select its variants), `--no-batch1` leaves it out.
 
-Other workloads (same JSON line): `qwen2` = BASELINE config 1 (Qwen2-0.5B, f32),
-`prefill` = BASELINE config 2 (one MoE layer over 2048 tokens on the tcgen05
-tensor cores; under torchrun expert-parallel with one NCCL all-reduce).
+Other workloads (same JSON line): `gptoss120b` = BASELINE config 4 (36 layers, 128 experts, 256 sequences, 4096-token
+contexts on a seeded synthetic KV cache), `qwen2` = config 1 (Qwen2-0.5B, f32), `prefill` = config 2 (one MoE layer
+over 2048 tokens on the tcgen05 tensor cores; under torchrun expert-parallel with one NCCL all-reduce).
+`--impl reference`: the C port of the reference's CPU path (oracle/model_oracle.c) timed on the host cores on real
+decode steps of the same model.
 """
 from __future__ import annotations
 
