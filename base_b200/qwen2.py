@@ -1,4 +1,4 @@
-"""Host side of the `native:qwen2` stage program (BASELINE config 1): config,
+"""Host side of the `native:qwen2` stage program (benchmark config 1): config,
 load header and a driver with the reference's decode protocol
 (lean/algorithms/Qwen2Common.lean:30, 830-864).  Host logic only."""
 from __future__ import annotations

@@ -5,7 +5,7 @@
                     [--workload gptoss|gptoss120b|qwen2|prefill] [--exchange peer|nccl]
                     [--step persistent|per-op] [--experts block-scaled|cuda-core] [--layers L] [--synthetic-kv]
 
-Default workload (BASELINE config 3 at batch 32): 24 layers, hidden 2880, 64 q / 8 kv heads of 64, sliding window 128
+Default workload (benchmark config 3 at batch 32): 24 layers, hidden 2880, 64 q / 8 kv heads of 64, sliding window 128
 alternating with full attention, sinks, 32 MXFP4 experts top-4, vocab 201088; random-init weights generated on the
 device from a seed; 32 sequences with 2048-token random prompts fed token by token (as the reference feeds prompts,
 lean/algorithms/Qwen2Common.lean:1446-1457), then K greedy tokens per sequence are timed.  A step = one decode step of
@@ -20,11 +20,11 @@ N > 1   one process per GPU (torchrun), ONE model sharded over the N GPUs: every
         experts' partial sums back to the sequences' owners, as NVLink stores from the producing kernels (--exchange
         peer) or as NCCL all-gather + all-to-all inside the graph (--exchange nccl).  The work is fixed as N grows
         ("scaling": "strong"); value = all sequences' tokens over the slowest rank's time.
-batch1  at N = 1 the line also carries BASELINE config 3 at batch 1 on the same GPU (`"batch1"`: the persistent
+batch1  at N = 1 the line also carries benchmark config 3 at batch 1 on the same GPU (`"batch1"`: the persistent
         cooperative kernel, with its own value, e2e, roofline and phase stamps); `--batch 1` runs only that (a replica
         per GPU under torchrun; --step / --experts select its variants), `--no-batch1` leaves it out.
 
-Other workloads (same JSON line): `gptoss120b` = BASELINE config 4 (36 layers, 128 experts, 256 sequences, 4096-token
+Other workloads (same JSON line): `gptoss120b` = benchmark config 4 (36 layers, 128 experts, 256 sequences, 4096-token
 contexts on a seeded synthetic KV cache), `qwen2` = config 1 (Qwen2-0.5B, f32), `prefill` = config 2 (one MoE layer
 over 2048 tokens on the tcgen05 tensor cores; under torchrun expert-parallel with one NCCL all-reduce).
 `--impl reference`: the C port of the reference's CPU path (oracle/model_oracle.c) timed on the host cores on real
@@ -226,7 +226,7 @@ def f32_to_bf16_values(x: np.ndarray) -> np.ndarray:
 
 
 def run_qwen2(a, rank: int):
-    """BASELINE config 1: Qwen2-0.5B shapes, f32 weights and cache, 32-token prompt fed
+    """benchmark config 1: Qwen2-0.5B shapes, f32 weights and cache, 32-token prompt fed
     token by token, K greedy tokens; single GPU by definition (rank 0 only)."""
     if rank != 0:
         return
@@ -264,7 +264,7 @@ def run_qwen2(a, rank: int):
     line = {"metric": "qwen2-0.5b f32 decode tok/s", "value": a.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": 1,
             "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms / a.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "Qwen2-0.5B decode, f32, batch 1, 32-token prompt, greedy (BASELINE config 1)",
+            "config": {"workload": "Qwen2-0.5B decode, f32, batch 1, 32-token prompt, greedy (benchmark config 1)",
                        "layers": cfg.layers, "hidden": cfg.hidden, "vocab": cfg.vocab, "context": prompt_len,
                        "step": "one launch per operation (CUDA graph)",
                        "l2": "each step streams ~2 GB of weights, far larger than L2; no flush needed"},
@@ -279,7 +279,7 @@ def run_qwen2(a, rank: int):
 
 
 def run_prefill(a, rank: int):
-    """BASELINE config 2: one gpt-oss-20b MoE layer over 2048 tokens (bf16 x, router skew
+    """benchmark config 2: one gpt-oss-20b MoE layer over 2048 tokens (bf16 x, router skew
     ~N(0,0.5) so the experts get uneven token counts), grouped GEMMs on the tcgen05 tensor
     cores.  A step = the whole layer (bf16 conversion, router, top-k, routing tables, gate_up,
     down, combine) once.  Under torchrun (N > 1) the layer is expert-parallel: rank r owns
@@ -302,7 +302,7 @@ def run_prefill(a, rank: int):
             peak, kind = float(json.loads(pj.read_text())["bf16_tflops"]), "measured"
         except Exception:
             pass
-    config = {"workload": "one gpt-oss-20b MoE FFN layer, 2048 tokens, top-4 of 32 experts, router skew 0.5 (BASELINE config 2)",
+    config = {"workload": "one gpt-oss-20b MoE FFN layer, 2048 tokens, top-4 of 32 experts, router skew 0.5 (benchmark config 2)",
               "tokens": T, "assignments": A,
               "l2": "the layer reads 424 MB of expert weights per step, larger than L2; no flush needed"}
     if world > 1:
@@ -410,7 +410,7 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--prompt", type=int, default=PROMPT)
     ap.add_argument("--batch", type=int, default=32,
-                    help="sequences decoded together, over all GPUs (default 32: BASELINE config 3 at batch 32, sharded over "
+                    help="sequences decoded together, over all GPUs (default 32: benchmark config 3 at batch 32, sharded over "
                          "the GPUs: strong scaling).  1 = the batch-1 persistent step kernel, a full replica per GPU")
     ap.add_argument("--no-batch1", action="store_true",
                     help="with --batch > 1 on one GPU: do not also measure the batch-1 persistent kernel")
@@ -421,8 +421,8 @@ def main():
     ap.add_argument("--synthetic-kv", action="store_true",
                     help="batched workloads: start from a seeded synthetic KV cache at the prompt length instead of feeding the prompt")
     ap.add_argument("--workload", choices=("gptoss", "gptoss120b", "qwen2", "prefill"), default="gptoss",
-                    help="gptoss: BASELINE config 3 (the headline); qwen2: BASELINE config 1 (Qwen2-0.5B f32, single GPU); "
-                         "prefill: BASELINE config 2 (one MoE layer, 2048 tokens, tensor cores)")
+                    help="gptoss: benchmark config 3 (the headline); qwen2: benchmark config 1 (Qwen2-0.5B f32, single GPU); "
+                         "prefill: benchmark config 2 (one MoE layer, 2048 tokens, tensor cores)")
     ap.add_argument("--exchange", choices=("peer", "nccl"), default="peer",
                     help="N > 1: the step's dispatch and combine as stores into peer memory by the kernels themselves, or NCCL")
     ap.add_argument("--step", choices=("persistent", "per-op"), default="persistent",
@@ -440,7 +440,7 @@ def main():
     if a.workload == "prefill":
         return run_prefill(a, rank)
     if a.workload == "gptoss120b":
-        # BASELINE config 4: gpt-oss-120b shapes (36 layers, 128 experts), batch 256, KV context 4096 (synthetic cache)
+        # benchmark config 4: gpt-oss-120b shapes (36 layers, 128 experts), batch 256, KV context 4096 (synthetic cache)
         if a.batch == 32:
             a.batch = 256
         if a.prompt == PROMPT:
@@ -453,7 +453,7 @@ def main():
 
 
 def run_batch1(a, rank: int, world: int, local: int, ranks=None, emit: bool = True):
-    """BASELINE config 3 at batch 1 per GPU: the persistent step kernel (or the per-operation graph); under
+    """benchmark config 3 at batch 1 per GPU: the persistent step kernel (or the per-operation graph); under
     torchrun every rank decodes its own sequence on a full replica (weak scaling, no data-path collective)."""
     from base_b200.gptoss import GPT_OSS_20B, GptOss, PDL, PERSISTENT, BLOCK_SCALED
     import dataclasses
@@ -462,7 +462,7 @@ def run_batch1(a, rank: int, world: int, local: int, ranks=None, emit: bool = Tr
                               flags=PDL | (PERSISTENT if a.step == "persistent" else 0) | (BLOCK_SCALED if mx else 0))
     if a.layers:
         cfg = dataclasses.replace(cfg, layers=a.layers)
-    config = {"workload": "gpt-oss-20b decode, batch 1 per GPU, 2048-token prompt, greedy (BASELINE config 3)",
+    config = {"workload": "gpt-oss-20b decode, batch 1 per GPU, 2048-token prompt, greedy (benchmark config 3)",
               "layers": cfg.layers, "hidden": cfg.hidden, "experts": cfg.experts, "top_k": cfg.top_k,
               "vocab": cfg.vocab, "context": a.prompt, "batch_per_gpu": 1,
               "parallelism": f"replicas x{a.gpus}" if a.gpus > 1 else "single GPU",
@@ -604,7 +604,7 @@ def run_batch1(a, rank: int, world: int, local: int, ranks=None, emit: bool = Tr
 
 
 def run_batched(a, rank: int, world: int, local: int):
-    """BASELINE config 3 at batch `--batch` (default 32): ONE model over all GPUs.  Every GPU holds batch / N of the
+    """benchmark config 3 at batch `--batch` (default 32): ONE model over all GPUs.  Every GPU holds batch / N of the
     sequences (their KV caches; attention and dense weights replicated) and experts / N of every layer's experts;
     per layer an all-gather of the normalised hidden states and an all-to-all of the experts' partial sums (NCCL,
     captured in the step's CUDA graph).  The work is fixed as N grows: strong scaling.  On one GPU the same
@@ -627,7 +627,7 @@ def run_batched(a, rank: int, world: int, local: int):
     metric = METRIC.replace("gpt-oss-20b", name)
     config = {"workload": f"{name} decode, {Bg} sequences, {a.prompt}-token " +
                           ("contexts (seeded synthetic KV cache)" if a.synthetic_kv else "prompts") +
-                          f", greedy (BASELINE config {'4' if big else '3'}, batch {Bg})",
+                          f", greedy (benchmark config {'4' if big else '3'}, batch {Bg})",
               "layers": cfg.layers, "hidden": cfg.hidden, "experts": cfg.experts, "top_k": cfg.top_k, "vocab": cfg.vocab,
               "context": a.prompt, "global_batch": Bg, "batch_per_gpu": per,
               "parallelism": f"expert parallel x{world}" if world > 1 else "single GPU",

@@ -3,7 +3,7 @@ INFRASTRUCTURE ONLY.
 
 Follows the reference's shipped decode program op by op
 (lean/algorithms/Qwen2Common.lean:1730-1749, args :1959-1997): rmsnorm
-(Qwen2Proven.lean:304-333; eps per BASELINE config 1 = 1e-6), q/k/v = W x + b
+(Qwen2Proven.lean:304-333; eps of benchmark config 1 = 1e-6), q/k/v = W x + b
 (:954-959), half-split RoPE on q and k from a host-built f32 table (:357-390,
 :522-560), KV store (:446-460), scores = 0.125 * K q, softmax with max shift,
 out = V^T p per q-head sharing its kv-head (lean/lib/AlgorithmLib/Cuda.lean:

@@ -170,7 +170,7 @@ def test_device_feedback_and_bounds_in_batched_mode():
 
 
 def test_batched_full_width_against_c_oracle():
-    """Two layers at the gpt-oss-20b widths, 32 sequences (BASELINE config 3 at batch 32): first positions, then
+    """Two layers at the gpt-oss-20b widths, 32 sequences (benchmark config 3 at batch 32): first positions, then
     context 2047 on the synthetic KV cache, three sequences against the C oracle."""
     from oracle import c_oracle
     c = GptOssConfig(layers=2, hidden=2880, inter=2880, experts=32, top_k=4, n_q=64, n_kv=8, vocab=4096, window=128,

@@ -219,7 +219,7 @@ def test_stage_errors_are_reported():
 
 @pytest.mark.parametrize("flags", [PDL, NO_RINGS, CKPT_LAYOUT])
 def test_gpt_oss_20b_layer_config0(flags):
-    # BASELINE config 0: hidden 2880, inter 2880, 32 experts, top-4, 1 decode token.
+    # benchmark config 0: hidden 2880, inter 2880, 32 experts, top-4, 1 decode token.
     cfg = MoeConfig()
     p = make_moe_params(cfg, seed=0)
     x = np.random.default_rng(1).standard_normal((1, cfg.hidden)).astype(np.float32)

@@ -129,7 +129,7 @@ def test_expert_range_needs_the_tensor_core_path():
 
 
 def test_config_2_at_full_size_against_the_oracle():
-    """BASELINE config 2 as the bench runs it: 2048 tokens, hidden = inter = 2880 (45 K steps, 192-row tiles over
+    """benchmark config 2 as the bench runs it: 2048 tokens, hidden = inter = 2880 (45 K steps, 192-row tiles over
     5760 and 2880 rows), 32 experts top-4, router skew 0.5 (uneven token counts).  Top-k indices and the token
     permutation bit-exact for all 8192 assignments; outputs within 1e-2 on tokens of the least and the most
     loaded expert, of the last (partial) token tile of the most loaded one, and a random sample."""

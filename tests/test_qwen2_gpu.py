@@ -1,5 +1,5 @@
 """Qwen2-architecture f32 decode through Base/execute_into vs the oracle
-(BASELINE config 1 shapes scaled down, plus one step at the real shapes).
+(benchmark config 1 shapes scaled down, plus one step at the real shapes).
 Tolerance: logits max|d|/max|ref| <= 1e-4 (f32); greedy tokens identical
 wherever the oracle's top-2 margin exceeds the bound."""
 import numpy as np
@@ -84,7 +84,7 @@ def test_one_step_at_qwen2_0_5b_shapes():
 
 
 def test_128_free_running_greedy_steps_at_config_1_widths():
-    """BASELINE config 1's protocol (32-token prompt, then 128 greedy tokens with the argmax fed back on the
+    """benchmark config 1's protocol (32-token prompt, then 128 greedy tokens with the argmax fed back on the
     device) at the Qwen2-0.5B widths with 4 of the 24 layers, against the C oracle fed the device's tokens: the
     oracle must pick the same token wherever its top-2 margin exceeds twice the logit bound, and a second
     instance replays the sequence step by step to check the bound itself at every step."""
