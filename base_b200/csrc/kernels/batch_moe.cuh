@@ -242,7 +242,9 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
   const uint32_t tmem = bars->tmem_base;
   // columns: the tokens' scales of two units in flight [0, 192), the weights' scales per ring slot (16 columns each) [192, 256), two accumulators [256, 512)
   const uint32_t tSFA = tmem, tSFB = tmem + 192, tD = tmem + 256;
-  pdl_wait();
+  // What the kernel before this one wrote (moe_expand_digits: the digits and the tokens' exponents) is not touched before
+  // pdl_wait() below.  The routing tables are older: moe_expand_digits itself waited for their kernel before it let this
+  // one start, so the units and the first weight copies do not wait (they overlap the digit expansion).
   pdl_launch_dependents();
 
   // ---- this CTA's units: all (expert, segment, pass) triples in that order, cut evenly over the grid
@@ -282,18 +284,45 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
   if (warp == 5) {
     // ---- producer
     if (lane == 0) {
-      uint32_t q = 0;
-      for (int ui = 0; ui < n_units; ++ui) {
+      auto emit = [&](uint32_t q, bool weights, bool digits) {
+        const BmUnit u = units[q / uint32_t(npair)];
+        const int p = int(q % uint32_t(npair));
+        const int off = offset[u.e] + u.pass * kBmTok, nt = min(kBmTok, count[u.e] - u.pass * kBmTok);
+        const uint8_t *wexp = W + size_t(u.e - a.lo) * mbytes;
+        const uint32_t s = q % n_slots;
+        const int c0 = 2 * p, nck = c0 + 1 < nch ? 2 : 1;
+        const int kc0 = min(kBmKc, kblocks - c0 * kBmKc), kc1 = nck == 2 ? min(kBmKc, kblocks - (c0 + 1) * kBmKc) : 0;
+        const uint32_t bb0 = uint32_t(seg16_bytes(kc0, u.ng)), bb1 = nck == 2 ? uint32_t(seg16_bytes(kc1, u.ng)) : 0u;
+        const uint32_t ab = uint32_t(nt * kBmKc * 128);
+        uint8_t *dst = ring + size_t(s) * slot_bytes;
+        if (weights) {
+          mbar_expect_tx(&bars->full[s], bb0 + bb1 + uint32_t(nck) * ab);
+          bulk_g2s(dst + 2 * a_bytes, wexp + seg16_offset(c0, u.g0 / kBmGroups, kc0, G), bb0, &bars->full[s]);
+          if (nck == 2) bulk_g2s(dst + 2 * a_bytes + kBmBBytes, wexp + seg16_offset(c0 + 1, u.g0 / kBmGroups, kc1, G), bb1, &bars->full[s]);
+        }
+        if (digits) {
+          bulk_g2s(dst, dig + (size_t(c0) * a.P + off) * (kBmKc * 128), ab, &bars->full[s]);
+          if (nck == 2) bulk_g2s(dst + a_bytes, dig + (size_t(c0 + 1) * a.P + off) * (kBmKc * 128), ab, &bars->full[s]);
+        }
+      };
+      const uint32_t total = uint32_t(n_units) * uint32_t(npair), head = min(n_slots, total);
+      for (uint32_t q = 0; q < head; ++q) emit(q, true, false);       // the first ring fill's weights: before the digits exist
+      pdl_wait();
+      for (uint32_t q = 0; q < head; ++q) emit(q, false, true);
+      // the steady state: plain nested loops (this one thread's instruction count is part of the kernel's pace)
+      uint32_t q = head;
+      int p = int(head % uint32_t(npair));
+      for (int ui = int(head / uint32_t(npair)); ui < n_units; ++ui, p = 0) {
         const BmUnit u = units[ui];
         const int off = offset[u.e] + u.pass * kBmTok, nt = min(kBmTok, count[u.e] - u.pass * kBmTok);
         const uint8_t *wexp = W + size_t(u.e - a.lo) * mbytes;
-        for (int p = 0; p < npair; ++p, ++q) {
+        const uint32_t ab = uint32_t(nt * kBmKc * 128);
+        for (; p < npair; ++p, ++q) {
           const uint32_t s = q % n_slots;
-          if (q >= n_slots && !bm_wait(&bars->empty[s], ((q / n_slots) - 1) & 1, bars, status, 72)) { ui = n_units; break; }
+          if (!bm_wait(&bars->empty[s], ((q / n_slots) - 1) & 1, bars, status, 72)) { ui = n_units; break; }
           const int c0 = 2 * p, nck = c0 + 1 < nch ? 2 : 1;
           const int kc0 = min(kBmKc, kblocks - c0 * kBmKc), kc1 = nck == 2 ? min(kBmKc, kblocks - (c0 + 1) * kBmKc) : 0;
           const uint32_t bb0 = uint32_t(seg16_bytes(kc0, u.ng)), bb1 = nck == 2 ? uint32_t(seg16_bytes(kc1, u.ng)) : 0u;
-          const uint32_t ab = uint32_t(nt * kBmKc * 128);
           uint8_t *dst = ring + size_t(s) * slot_bytes;
           mbar_expect_tx(&bars->full[s], bb0 + bb1 + uint32_t(nck) * ab);
           bulk_g2s(dst + 2 * a_bytes, wexp + seg16_offset(c0, u.g0 / kBmGroups, kc0, G), bb0, &bars->full[s]);
@@ -369,6 +398,7 @@ B200_DEVICE void batch_mx_body(const uint8_t *__restrict__ W, const float *__res
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->uready[ui & 1]);
     };
+    pdl_wait();                                  // the tokens' exponents come from the kernel before
     if (n_units > 0) stage_scales(0);
     for (int ui = 0; ui < n_units; ++ui) {
       const BmUnit u = units[ui];
