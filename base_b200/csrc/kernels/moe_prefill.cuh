@@ -464,13 +464,19 @@ moe_topk_tables_many(const float *__restrict__ logits, int *__restrict__ topk_id
     for (int i = na + lane; i < E; i += 32) active[i] = -1;
   }
   __syncthreads();
-  for (int e = warp; e < E; e += 32) {
-    int at = s_offset[e];
-    for (int base = 0; base < A; base += 32) {
-      const bool mine = base + lane < A && s_idx[base + lane] == e;
+  // warp w writes the permutation of experts w, w + 32, w + 64, w + 96 in one walk over the assignments
+  int at[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) at[j] = warp + 32 * j < E ? s_offset[warp + 32 * j] : 0;
+  const unsigned below = (1u << lane) - 1u;
+  for (int base = 0; base < A; base += 32) {
+    const int e = base + lane < A ? s_idx[base + lane] : -1;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const bool mine = e == warp + 32 * j;
       const unsigned m = __ballot_sync(0xffffffffu, mine);
-      if (mine) perm[at + __popc(m & ((1u << lane) - 1u))] = base + lane;
-      at += __popc(m);
+      if (mine) perm[at[j] + __popc(m & below)] = base + lane;
+      at[j] += __popc(m);
     }
   }
 }
