@@ -722,7 +722,10 @@ def run_batched(a, rank: int, world: int, local: int):
     step_s = ms * 1e-3 / a.steps
     achieved = gu_bytes / per_launch(gu_ms) / 1e9
     roof = {"kernel": "moe_batch_mx_gate_up", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-            "frac": achieved / peak, "peak_source": peak_kind, "traffic": None,
+            "frac": achieved / peak, "peak_source": peak_kind,
+            # dram__bytes_read + write of one launch, from the ncu capture of this kernel on a 2-layer model of the 20b
+            # widths (profiles/moe_batch_mx_gate_up_ncu_full.md): a launch there is a layer's experts, as here
+            "traffic": 280925952 if (not big and world == 1 and Bg == 32) else None,
             "bytes_per_launch": gu_bytes, "us_per_launch": per_launch(gu_ms) * 1e6, "experts_hit_per_gpu": hit,
             "other_kernels": {"moe_batch_mx_down": {"gbs": dn_bytes / per_launch(dn_ms) / 1e9, "us_per_launch": per_launch(dn_ms) * 1e6},
                               "dense_tc_gemm_qkv": {"gbs": qkv_bytes / per_launch(qkv_ms) / 1e9, "us_per_launch": per_launch(qkv_ms) * 1e6},
