@@ -138,3 +138,23 @@ def test_expert_parallel_exchange_on_two_ranks_equals_the_unsharded_layer():
         assert err < 1e-6                                    # same products, summed per rank then over ranks
         assert all(lo <= e < lo + n for e in used) and used  # a rank only ever runs its own experts
         assert ident == b"id-from-0"
+
+
+def test_exchange_counters_reach_their_targets_round_by_round():
+    """The arithmetic of the kernels' own exchange (csrc/kernels/peer_xchg.cuh), restated on the host: every source rank
+    adds one arrival per sequence and round to a counter that never resets; a consumer of round (step, layer) waits
+    for ((step - 1) * layers + layer + 1) * per_round.  The target must be exactly what has arrived once the round is
+    complete, and must not be reachable one arrival earlier (a consumer can then never run ahead of a producer)."""
+    layers, per_round, world = 5, 3, 4
+    counters = [0] * world                     # one rank's view: arrivals from every source rank
+    for step in range(1, 4):                   # the step counter is bumped before the first layer: 1-based
+        for layer in range(layers):
+            target = ((step - 1) * layers + layer + 1) * per_round
+            for src in range(world):
+                for seq in range(per_round):
+                    assert counters[src] - target < 0            # not yet: the wait would still be spinning
+                    counters[src] += 1
+            assert all(c - target >= 0 for c in counters) and all(c == target for c in counters)
+    # 32-bit wrap: the comparison is on the signed difference
+    wrap = lambda v: (v + 2 ** 31) % 2 ** 32 - 2 ** 31
+    assert wrap((2 ** 32 + 5) % 2 ** 32 - (2 ** 32 - 3) % 2 ** 32) >= 0 and wrap((2 ** 32 - 3) - (2 ** 32 + 5)) < 0
