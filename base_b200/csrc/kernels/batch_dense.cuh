@@ -209,10 +209,11 @@ dense_tc_gemm(const uint8_t *__restrict__ Wt, const uint8_t *__restrict__ At, co
   // producer, tensor core and back (two mbarrier waits, a commit) costs about 0.25 us whatever the slot holds, and
   // with one chunk per slot that, not bytes or instructions, was the kernel's time (measured by leaving the A copies
   // and the instructions out: 17 of 20 us stayed).
-  // kc = 2 chunks per slot, or 3 / 4 where four such slots still fit the ring (few tokens, few rows per CTA).
+  // kc = 2 chunks per slot, or 3 / 4 where three such slots still fit the ring (measured at 32 tokens: qkv 15.1 us with
+  // kc = 2 and five slots, 12.9 with kc = 3 and three slots, 13.9 with kc = 4 and two).
   const uint32_t b_max = uint32_t(max(1, min(kBdMaxGroups, g_hi - g_lo))) * 1024u;
   int kc = 2;
-  while (kc < 4 && uint32_t(kc + 1) * (a_bytes + b_max) * 4u <= uint32_t(kBdRingBytes)) ++kc;
+  while (kc < 4 && uint32_t(kc + 1) * (a_bytes + b_max) * 3u <= uint32_t(kBdRingBytes)) ++kc;
   const uint32_t slot_bytes = uint32_t(kc) * (a_bytes + b_max);
   const uint32_t n_slots = min(uint32_t(kBdSlots), uint32_t(kBdRingBytes) / slot_bytes);
   const int npairs = (nchunks + kc - 1) / kc;
