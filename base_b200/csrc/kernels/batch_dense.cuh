@@ -22,7 +22,7 @@ constexpr int kBdTokens = 32;          // tokens per pass
 constexpr int kBdRows = 64;            // A rows per pass (hi + lo)
 constexpr int kBdMaxGroups = 16;       // row groups per unit: N <= 128
 constexpr int kBdSlots = 16;          // at most; the ring holds as many slots as fit (a slot = the A piece + this CTA's B piece of one K chunk)
-constexpr int kBdRingBytes = 6 * (8192 + kBdMaxGroups * 1024);
+constexpr int kBdRingBytes = 8 * (8192 + kBdMaxGroups * 1024);      // 192 KB
 constexpr int kBdThreads = 192;        // warps 0..3: epilogue, warp 4: producer, warp 5: issuer
 constexpr uint32_t kBdSpin = 1u << 22;
 
@@ -202,7 +202,8 @@ dense_tc_gemm(const uint8_t *__restrict__ Wt, const uint8_t *__restrict__ At, co
   const int RG = a.rows >> 3, nchunks = a.K >> 6, passes = (a.B + kBdTokens - 1) / kBdTokens;
   const int g_lo = int((long long)RG * blockIdx.x / gridDim.x), g_hi = int((long long)RG * (blockIdx.x + 1) / gridDim.x);
   const int units = (g_hi - g_lo + kBdMaxGroups - 1) / kBdMaxGroups, jobs = units * passes;
-  // few rows per CTA (qkv, o-proj): small slots, many of them in flight; many rows (lm_head): 6 slots of 24 KB
+  // the ring is 192 KB (all the shared memory the staging rows and barriers leave): lm_head runs four slots of two
+  // 24 KB chunks, qkv / o-proj four or five slots of three chunks
   const int Rh = bd_rh(a.B);
   const uint32_t a_bytes = 256u * uint32_t(Rh);                // the A tile of one pass and K chunk
   // A ring slot holds kc >= 2 consecutive K chunks (the last slot what is left): the hand-over of a slot between

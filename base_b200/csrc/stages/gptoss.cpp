@@ -102,7 +102,7 @@ struct RouterPeerArgs { RouterManyArgs r; int tag, layers, per_round; };
 struct CombinePeersArgs { int H, top_k, lo, n, B, tag, layers; };
 struct RowsToAPeerArgs { RowsToAArgs r; int tag, layers; };
 struct RetileSegArgs { int R, K, n_mat; };
-constexpr int kBdThreads = 192, kBdSmemBytes = 6 * (8192 + 16 * 1024) + 64 * 129 * 4 + 512;
+constexpr int kBdThreads = 192, kBdSmemBytes = 8 * (8192 + 16 * 1024) + 64 * 129 * 4 + 512;
 constexpr int kBmThreads = 192, kBmSmemBytes = 8 * (16 * (8 * 128 + 64) + 8 * 8 * 128) + 192 * 8 + 4096;
 struct SynthArgs { unsigned long long n; uint32_t tensor, seed; int kind; float c; int lo, span; unsigned long long first; };
 

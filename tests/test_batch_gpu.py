@@ -56,7 +56,7 @@ def run_gemm(L, c, rows, K, B, kind, rows16, grid, rng):
 
     launch(b"dense_tc_retile", [b["w"], b["wt"]], struct.pack("<2i", rows, K), 64, 256)
     launch(b"rows_to_a", [b["x"], -1, -1, -1, -1, b["at"]], struct.pack("<4iqf4x", K, B, 0, 0, 0, 1e-5), B, 256)
-    smem = 6 * (8192 + 16 * 1024) + 64 * 129 * 4 + 512
+    smem = 8 * (8192 + 16 * 1024) + 64 * 129 * 4 + 512
     launch(b"dense_tc_gemm", [b["wt"], b["at"], b["bias"], b["res"], b["out"], b["st"]],
            struct.pack("<6i", rows, K, B, kind, rows16, rows), grid, 192, smem)
     assert L.cl_cuda_sync(c) == 0, L.cl_b200_last_error().decode()
