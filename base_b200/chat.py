@@ -12,8 +12,8 @@ A line that would not fit the context (system prompt + line bytes + wrapper + MA
 byte being the worst case) is refused, as the reference's derived input limit does.
 
 `python -m base_b200.chat --tokenizer FILE` runs the loop on stdin/stdout over the `native:qwen2` stage program with
-the Qwen2-0.5B shapes.  Without real weights (this build generates them from a seed) the answers are noise; the
-module exists for the protocol and is tested against a scripted decoder.
+the Qwen2-0.5B shapes; `--weights FILE` loads a flat f32 weight file in the reference's layout (without it the weights
+are generated from a seed and the answers are noise).  The protocol is tested against a scripted decoder.
 """
 from __future__ import annotations
 
@@ -79,12 +79,17 @@ class ChatSession:
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--tokenizer", required=True, help="tokenizer file in the reference's format (base_b200.tokenizer)")
-    ap.add_argument("--seed", type=int, default=3, help="seed of the generated Qwen2-0.5B-shaped weights")
+    ap.add_argument("--weights", help="flat f32 weight file in the reference's layout (base_b200.convert.write_qwen2_flat); "
+                                      "without it the Qwen2-0.5B-shaped weights are generated from --seed and the answers are noise")
+    ap.add_argument("--seed", type=int, default=3, help="seed of the generated weights")
     a = ap.parse_args()
     from .qwen2 import QWEN2_0_5B, Qwen2
     import dataclasses
     tok = Tokenizer.load(a.tokenizer)
     model = Qwen2(dataclasses.replace(QWEN2_0_5B, seed=a.seed, max_seq=2048))
+    if a.weights:
+        from .convert import load_qwen2_flat
+        load_qwen2_flat(model, a.weights)
     session = ChatSession(lambda t, p: int(model.infer([t], [p])[0]), tok, max_seq=2048)
     try:
         for line in sys.stdin.buffer:

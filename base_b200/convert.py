@@ -188,3 +188,91 @@ def from_hf_state_dict(sd: dict, cfg: GptOssConfig) -> dict:
             "dn_codes": dn_b.reshape(*dn_b.shape[:2], -1), "dn_scales": g(m + "experts.down_proj_scales"),
             "dn_bias": g(m + "experts.down_proj_bias").astype(np.float32)})
     return w
+
+
+# ---- Qwen2: the reference's flat f32 weight file -------------------------------------------------------------------
+# tools/qwen2_convert.py:12-28, 101-141: f32 little endian, no header, in this order: embed_tokens [vocab][hidden]; per
+# layer rms_attn [hidden], q_proj weight [n_q*64][hidden] and bias, k_proj weight [n_kv*64][hidden] and bias, v_proj
+# weight and bias, o_proj weight [hidden][n_q*64], rms_ffn [hidden], gate_proj [inter][hidden], up_proj [inter][hidden],
+# down_proj [hidden][inter]; then rms_final [hidden] and lm_head [vocab][hidden] (a copy of embed_tokens for the 0.5B
+# model, which ties them).
+
+def qwen2_flat_layout(cfg):
+    """[(name, layer or None, shape)] in file order for a base_b200.qwen2.Qwen2Config."""
+    H, F, QD, KVD, V = cfg.hidden, cfg.inter, cfg.n_q * cfg.head_dim, cfg.n_kv * cfg.head_dim, cfg.vocab
+    out = [("embed", None, (V, H))]
+    for l in range(cfg.layers):
+        out += [("ln1", l, (H,)), ("wq", l, (QD, H)), ("bq", l, (QD,)), ("wk", l, (KVD, H)), ("bk", l, (KVD,)),
+                ("wv", l, (KVD, H)), ("bv", l, (KVD,)), ("wo", l, (H, QD)), ("ln2", l, (H,)), ("wgate", l, (F, H)),
+                ("wup", l, (F, H)), ("wdn", l, (H, F))]
+    out += [("lnf", None, (H,)), ("lm_head", None, (V, H))]
+    return out
+
+
+def qwen2_flat_bytes(cfg) -> int:
+    return 4 * sum(int(np.prod(shape)) for _, _, shape in qwen2_flat_layout(cfg))
+
+
+def write_qwen2_flat(path, cfg, tensors: dict) -> None:
+    """tensors: {(name, layer or None): array} with the names of qwen2_flat_layout."""
+    with open(path, "wb") as f:
+        for name, layer, shape in qwen2_flat_layout(cfg):
+            a = np.asarray(tensors[(name, layer)], dtype="<f4")
+            if a.shape != shape:
+                raise ValueError(f"{name} of layer {layer}: shape {a.shape}, expected {shape}")
+            f.write(a.tobytes())
+
+
+def read_qwen2_flat(path, cfg) -> dict:
+    """The file as {(name, layer or None): read-only array view} (memory-mapped)."""
+    import os
+    need = qwen2_flat_bytes(cfg)
+    if os.path.getsize(path) != need:
+        raise ValueError(f"{path}: {os.path.getsize(path)} bytes, the configuration needs {need}")
+    mm = np.memmap(path, dtype="<f4", mode="r")
+    out, at = {}, 0
+    for name, layer, shape in qwen2_flat_layout(cfg):
+        n = int(np.prod(shape))
+        out[(name, layer)] = mm[at:at + n].reshape(shape)
+        at += n
+    return out
+
+
+def qwen2_stage_tensors(cfg, flat: dict):
+    """The stage program's tensors from the file's: yields (layer, kind, array) with wqkv = [q; k; v] rows and
+    wgu = [gate; up] rows (layer 1000 = globals).  The stage ties lm_head to the embedding, as Qwen2-0.5B does: a
+    file whose lm_head differs from its embedding is refused."""
+    if not np.array_equal(flat[("embed", None)], flat[("lm_head", None)]):
+        raise ValueError("lm_head differs from embed_tokens: the qwen2 stage program ties them")
+    yield 1000, "embed", flat[("embed", None)]
+    yield 1000, "lnf", flat[("lnf", None)]
+    for l in range(cfg.layers):
+        yield l, "ln1", flat[("ln1", l)]
+        yield l, "wqkv", np.concatenate([flat[("wq", l)], flat[("wk", l)], flat[("wv", l)]], axis=0)
+        yield l, "bqkv", np.concatenate([flat[("bq", l)], flat[("bk", l)], flat[("bv", l)]], axis=0)
+        yield l, "wo", flat[("wo", l)]
+        yield l, "ln2", flat[("ln2", l)]
+        yield l, "wgu", np.concatenate([flat[("wgate", l)], flat[("wup", l)]], axis=0)
+        yield l, "wdn", flat[("wdn", l)]
+
+
+def load_qwen2_flat(model, path) -> None:
+    """Replace the seeded weights of a base_b200.qwen2.Qwen2 instance by those of a flat weight file."""
+    for layer, kind, a in qwen2_stage_tensors(model.cfg, read_qwen2_flat(path, model.cfg)):
+        model.set_tensor(layer, kind, a)
+
+
+def qwen2_flat_from_hf_state_dict(sd: dict, cfg) -> dict:
+    """Hugging Face Qwen2 parameter names -> the file's tensors (tools/qwen2_convert.py:113-137)."""
+    g = lambda k: np.asarray(sd[k], dtype=np.float32)
+    out = {("embed", None): g("model.embed_tokens.weight"), ("lnf", None): g("model.norm.weight")}
+    out[("lm_head", None)] = g("lm_head.weight") if "lm_head.weight" in sd else out[("embed", None)]
+    for l in range(cfg.layers):
+        p = f"model.layers.{l}"
+        out.update({("ln1", l): g(f"{p}.input_layernorm.weight"), ("wq", l): g(f"{p}.self_attn.q_proj.weight"),
+                    ("bq", l): g(f"{p}.self_attn.q_proj.bias"), ("wk", l): g(f"{p}.self_attn.k_proj.weight"),
+                    ("bk", l): g(f"{p}.self_attn.k_proj.bias"), ("wv", l): g(f"{p}.self_attn.v_proj.weight"),
+                    ("bv", l): g(f"{p}.self_attn.v_proj.bias"), ("wo", l): g(f"{p}.self_attn.o_proj.weight"),
+                    ("ln2", l): g(f"{p}.post_attention_layernorm.weight"), ("wgate", l): g(f"{p}.mlp.gate_proj.weight"),
+                    ("wup", l): g(f"{p}.mlp.up_proj.weight"), ("wdn", l): g(f"{p}.mlp.down_proj.weight")})
+    return out

@@ -370,6 +370,31 @@ void stage_fetch_tensor(uint8_t *mem) {
     return stage_fail(mem, 2, std::string("fetchTensor: ") + cl_b200_last_error());
 }
 
+// setTensor: data = [layer:u32][kind:u32] (as fetchTensor) followed by the tensor's f32 bytes in the layout fetchTensor
+// returns (row-major [out][in]; wqkv = [q; k; v] rows, wgu = [gate; up] rows, the embedding doubles as lm_head): real
+// weights replace the seeded ones (the reference's flat weight file, tools/qwen2_convert.py:12-28, is such tensors in a
+// fixed order; base_b200/convert.py reads it).  The step's captured graph stays valid: the buffers do not move.
+void stage_set_tensor(uint8_t *mem) {
+  StageIO io(mem);
+  State *s = io.state<State>();
+  if (!s) return stage_fail(mem, 1, "setTensor: load has not run");
+  if (io.data_len < 8) return stage_fail(mem, 1, "setTensor: data must be [layer, kind] + bytes");
+  uint32_t q[2];
+  memcpy(q, io.data, 8);
+  int buf = -1;
+  if (q[0] == 1000) buf = q[1] == kEmbed ? s->embed : q[1] == kLnF ? s->lnf : -1;
+  else if (q[0] < s->h.layers) {
+    const Layer &ly = s->layers[q[0]];
+    const int t[] = {ly.ln1, ly.wqkv, ly.bqkv, ly.wo, ly.ln2, ly.wgu, ly.wdn};
+    if (q[1] < 7) buf = t[q[1]];
+  }
+  if (buf < 0) return stage_fail(mem, 1, "setTensor: no such tensor");
+  const int64_t bytes = int64_t(io.data_len) - 8;
+  if (bytes != cl_b200_buffer_size(io.ctx(), buf)) return stage_fail(mem, 1, "setTensor: wrong size for this tensor");
+  if (cl_cuda_sync(io.ctx()) != 0 || cl_cuda_upload_ptr(io.ctx(), buf, io.data + 8, bytes) != 0)
+    return stage_fail(mem, 2, std::string("setTensor: ") + cl_b200_last_error());
+}
+
 void destroy(uint8_t *mem) {
   StageIO io(mem);
   State *s = io.state<State>();
@@ -387,7 +412,7 @@ struct Registrar {
     p.name = "qwen2";
     p.stages = {{"", stage_noop},       {"load", stage_load},     {"prep", stage_prep},
                 {"infer", stage_infer}, {"decode", stage_decode}, {"fetchLogits", stage_fetch_logits},
-                {"fetchTensor", stage_fetch_tensor}};
+                {"fetchTensor", stage_fetch_tensor}, {"setTensor", stage_set_tensor}};
     p.destroy = destroy;
     register_plugin(p);
   }

@@ -85,5 +85,10 @@ class Qwen2:
         self.base.execute_into(self.art.extras["fetchTensor"], struct.pack("<2I", layer, KIND[kind]), out)
         return np.frombuffer(bytes(out), dtype="<f4")
 
+    def set_tensor(self, layer: int, kind: str, values) -> None:
+        """Replace a seeded tensor by real f32 weights (stage `setTensor`; layout as `tensor` returns it)."""
+        a = np.ascontiguousarray(values, dtype="<f4")
+        self.base.execute(self.art.extras["setTensor"], struct.pack("<2I", layer, KIND[kind]) + a.tobytes())
+
     def close(self):
         self.base.close()

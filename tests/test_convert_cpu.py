@@ -99,3 +99,78 @@ def test_hugging_face_names_map_onto_the_weights_dict():
         np.testing.assert_array_equal(got[k], w[k])
     for k, _, _ in cv._LAYER:
         np.testing.assert_array_equal(got["layers"][0][k], ly[k], err_msg=k)
+
+
+# ---- Qwen2: the reference's flat f32 weight file ---------------------------------------------------------------------
+def qwen2_tiny():
+    from base_b200.qwen2 import Qwen2Config
+    return Qwen2Config(layers=2, hidden=64, inter=128, n_q=2, n_kv=1, vocab=96, max_seq=32)
+
+
+def qwen2_random_flat(c, seed=9, tie=True):
+    rng = np.random.default_rng(seed)
+    flat = {(n, l): rng.standard_normal(shape).astype(np.float32) * np.float32(0.05) for n, l, shape in cv.qwen2_flat_layout(c)}
+    for key in list(flat):
+        if key[0] in ("ln1", "ln2", "lnf"):
+            flat[key] = (flat[key] + 1).astype(np.float32)
+    if tie:
+        flat[("lm_head", None)] = flat[("embed", None)]
+    return flat
+
+
+def test_qwen2_flat_file_order_sizes_and_round_trip(tmp_path):
+    from base_b200.qwen2 import QWEN2_0_5B
+    c = qwen2_tiny()
+    names = [n for n, _, _ in cv.qwen2_flat_layout(c)]
+    per_layer = ["ln1", "wq", "bq", "wk", "bk", "wv", "bv", "wo", "ln2", "wgate", "wup", "wdn"]      # the converter's write order
+    assert names == ["embed"] + per_layer * c.layers + ["lnf", "lm_head"]
+    assert cv.qwen2_flat_bytes(QWEN2_0_5B) == 4 * (2 * 151936 * 896 + 896 + 24 * (
+        2 * 896 + 896 * 896 + 896 + 2 * (128 * 896 + 128) + 896 * 896 + 3 * 4864 * 896))
+    flat = qwen2_random_flat(c)
+    p = tmp_path / "w.bin"
+    cv.write_qwen2_flat(p, c, flat)
+    assert p.stat().st_size == cv.qwen2_flat_bytes(c)
+    back = cv.read_qwen2_flat(p, c)
+    for key, a in flat.items():
+        np.testing.assert_array_equal(back[key], a)
+    raw = np.fromfile(p, dtype="<f4")
+    np.testing.assert_array_equal(raw[:c.vocab * c.hidden], flat[("embed", None)].ravel())             # first in the file
+    np.testing.assert_array_equal(raw[-c.vocab * c.hidden:], flat[("lm_head", None)].ravel())          # last
+    with open(p, "ab") as f:
+        f.write(b"\0\0\0\0")
+    with pytest.raises(ValueError):
+        cv.read_qwen2_flat(p, c)
+
+
+def test_qwen2_stage_tensors_concatenate_projections_and_refuse_an_untied_head():
+    c = qwen2_tiny()
+    flat = qwen2_random_flat(c)
+    got = {(l, k): a for l, k, a in cv.qwen2_stage_tensors(c, flat)}
+    assert set(k for _, k in got) == {"embed", "lnf", "ln1", "wqkv", "bqkv", "wo", "ln2", "wgu", "wdn"}
+    qd, kvd = c.n_q * 64, c.n_kv * 64
+    w = got[(1, "wqkv")]
+    assert w.shape == (qd + 2 * kvd, c.hidden)
+    np.testing.assert_array_equal(w[:qd], flat[("wq", 1)])
+    np.testing.assert_array_equal(w[qd:qd + kvd], flat[("wk", 1)])
+    np.testing.assert_array_equal(w[qd + kvd:], flat[("wv", 1)])
+    np.testing.assert_array_equal(got[(0, "wgu")][:c.inter], flat[("wgate", 0)])
+    np.testing.assert_array_equal(got[(0, "wgu")][c.inter:], flat[("wup", 0)])
+    np.testing.assert_array_equal(got[(0, "bqkv")], np.concatenate([flat[("bq", 0)], flat[("bk", 0)], flat[("bv", 0)]]))
+    with pytest.raises(ValueError):
+        list(cv.qwen2_stage_tensors(c, qwen2_random_flat(c, tie=False)))
+
+
+def test_qwen2_hf_names_map_to_the_file():
+    c = qwen2_tiny()
+    flat = qwen2_random_flat(c)
+    hf = {"model.embed_tokens.weight": flat[("embed", None)], "model.norm.weight": flat[("lnf", None)]}
+    names = dict(ln1="input_layernorm.weight", wq="self_attn.q_proj.weight", bq="self_attn.q_proj.bias", wk="self_attn.k_proj.weight",
+                 bk="self_attn.k_proj.bias", wv="self_attn.v_proj.weight", bv="self_attn.v_proj.bias", wo="self_attn.o_proj.weight",
+                 ln2="post_attention_layernorm.weight", wgate="mlp.gate_proj.weight", wup="mlp.up_proj.weight", wdn="mlp.down_proj.weight")
+    for l in range(c.layers):
+        for k, n in names.items():
+            hf[f"model.layers.{l}.{n}"] = flat[(k, l)]
+    back = cv.qwen2_flat_from_hf_state_dict(hf, c)                  # no lm_head.weight: tied to the embedding
+    assert set(back) == set(flat)
+    for key in flat:
+        np.testing.assert_array_equal(back[key], flat[key])

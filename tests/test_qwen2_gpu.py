@@ -129,3 +129,47 @@ def test_steps_past_the_end_of_the_cache_are_refused():
     m.base.execute(m.art.main, c.header())       # load again on a loaded instance
     assert m.infer([1], [0]).shape == (1,)
     m.close()
+
+
+def test_weights_from_a_flat_file_replace_the_seeded_ones(tmp_path):
+    """The reference's flat f32 weight file (tools/qwen2_convert.py:12-28) written with random tensors, loaded through the
+    `setTensor` stage: the device reads back exactly what the file holds, and decodes like the oracle given the same
+    tensors (not like the seeded model)."""
+    from base_b200 import convert as cv
+    c = small(layers=2, vocab=320)
+    rng = np.random.default_rng(17)
+    flat = {(n, l): (rng.standard_normal(shape) * 0.05).astype(np.float32) for n, l, shape in cv.qwen2_flat_layout(c)}
+    for key in list(flat):
+        if key[0] in ("ln1", "ln2", "lnf"):
+            flat[key] = (flat[key] + 1).astype(np.float32)
+    flat[("lm_head", None)] = flat[("embed", None)]
+    path = tmp_path / "qwen2.bin"
+    cv.write_qwen2_flat(path, c, flat)
+    m = Qwen2(c)
+    seeded = int(m.infer([5], [0])[0])
+    seeded_logits = m.logits()[0].copy()
+    cv.load_qwen2_flat(m, path)
+    stage = {(l, k): np.asarray(a) for l, k, a in cv.qwen2_stage_tensors(c, cv.read_qwen2_flat(path, c))}
+    np.testing.assert_array_equal(m.tensor(1, "wgu", stage[(1, "wgu")].size), stage[(1, "wgu")].ravel())
+    np.testing.assert_array_equal(m.tensor(1000, "embed", stage[(1000, "embed")].size), stage[(1000, "embed")].ravel())
+    w = {"embed": stage[(1000, "embed")], "lnf": stage[(1000, "lnf")],
+         "layers": [{k: stage[(l, k)] for k in ("ln1", "wqkv", "bqkv", "wo", "ln2", "wgu", "wdn")} for l in range(c.layers)]}
+    o = qo.Model(ocfg(c), w)
+    tok = 5
+    for pos in range(6):
+        want, ref = o.step(tok, pos, return_logits=True)
+        got = int(m.infer([tok], [pos])[0])
+        logits = m.logits()[0]
+        assert rel(logits, ref) < TOL, f"pos {pos}: {rel(logits, ref)}"
+        top2 = np.sort(ref)[-2:]
+        if top2[1] - top2[0] > 4 * TOL * np.abs(ref).max():
+            assert got == want
+        if pos == 0:
+            assert rel(logits, seeded_logits) > 1e-2          # these are not the seeded model's logits any more
+        tok = want
+    with pytest.raises(RuntimeError, match="wrong size"):
+        m.set_tensor(0, "ln1", np.zeros(3, np.float32))
+    with pytest.raises(RuntimeError, match="no such tensor"):
+        m.base.execute(m.art.extras["setTensor"], b"\x07\x00\x00\x00\x09\x00\x00\x00" + b"\0" * 4)
+    m.close()
+    del seeded
