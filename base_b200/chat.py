@@ -82,14 +82,23 @@ def main() -> None:
     ap.add_argument("--weights", help="flat f32 weight file in the reference's layout (base_b200.convert.write_qwen2_flat); "
                                       "without it the Qwen2-0.5B-shaped weights are generated from --seed and the answers are noise")
     ap.add_argument("--seed", type=int, default=3, help="seed of the generated weights")
+    ap.add_argument("--on-disk", metavar="CACHE_FILE",
+                    help="the reference's second binary (qwen2_on_disk): one layer's weights and one K/V pair on the device, the "
+                         "layers streamed from --weights every step and the KV cache kept in CACHE_FILE; same answers")
     a = ap.parse_args()
-    from .qwen2 import QWEN2_0_5B, Qwen2
+    from .qwen2 import ON_DISK, QWEN2_0_5B, Qwen2
     import dataclasses
     tok = Tokenizer.load(a.tokenizer)
-    model = Qwen2(dataclasses.replace(QWEN2_0_5B, seed=a.seed, max_seq=2048))
-    if a.weights:
-        from .convert import load_qwen2_flat
-        load_qwen2_flat(model, a.weights)
+    if a.on_disk:
+        if not a.weights:
+            ap.error("--on-disk needs --weights")
+        model = Qwen2(dataclasses.replace(QWEN2_0_5B, max_seq=2048, flags=QWEN2_0_5B.flags | ON_DISK))
+        model.open_files(a.weights, a.on_disk)
+    else:
+        model = Qwen2(dataclasses.replace(QWEN2_0_5B, seed=a.seed, max_seq=2048))
+        if a.weights:
+            from .convert import load_qwen2_flat
+            load_qwen2_flat(model, a.weights)
     session = ChatSession(lambda t, p: int(model.infer([t], [p])[0]), tok, max_seq=2048)
     try:
         for line in sys.stdin.buffer:

@@ -15,6 +15,10 @@
 //   SiLU(gate)*up + down GEMV + residual
 // then final norm + tied lm_head GEMV, and the first-index argmax.
 // Weights are synthetic (kernels/synth.cuh), f32 ~ N(0, 0.02), tied embeddings.
+#include <fcntl.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
 #include <algorithm>
 #include <cmath>
 #include <cstdlib>
@@ -31,7 +35,7 @@ struct QwenHeader {
   uint32_t magic;        // 'QW21'
   uint32_t layers, hidden, inter, n_q, n_kv, head_dim, vocab, max_seq, batch;
   float rope_theta, eps;
-  uint32_t seed, flags;  // flags bit 0: programmatic dependent launch
+  uint32_t seed, flags;  // flags bit 0: programmatic dependent launch; bit 3: weights and KV cache stay on disk (openFiles)
   uint32_t reserved[2];
 };
 static_assert(sizeof(QwenHeader) == 64, "header is 64 bytes");
@@ -65,6 +69,10 @@ struct State {
   int dense_stream = 1;
   LoadScope scope;
   std::vector<int64_t> next_pos;     // per sequence: the position the next step runs at
+  // on-disk mode (header flags bit 3): ONE layer's weights and ONE K/V pair live on the device (layers[0]); every step
+  // streams each layer's weights from the weight file and its K/V rows from the cache file, and writes the new row back
+  int on_disk = 0, wfd = -1, kvfd = -1;
+  std::vector<uint8_t> host;
 };
 
 constexpr int kArgmaxParts = 128;
@@ -97,15 +105,29 @@ void launch_gemv(State *s, Launcher &L, std::initializer_list<int32_t> bufs9, Ge
     xbytes + 4 * stages * row_bytes + 4 * stages * 8, pdl);
 }
 
+void enqueue_layer(State *s, Launcher &L, const Layer &ly);
+void enqueue_tail(State *s, Launcher &L);
+
+void enqueue_head(State *s, Launcher &L) {
+  const QwenHeader &h = s->h;
+  const int pdl = (h.flags & 1) ? 1 : 0;
+  EmbedArgs ea{int(h.hidden), int(h.batch), 1, int(h.vocab)};
+  L("embed_gather", {s->embed, s->meta, s->hA}, ea, (int(h.hidden) + 255) / 256, int(h.batch), 1, 256, 0, pdl);
+}
+
 void enqueue_step(State *s, Launcher &L) {
   const QwenHeader &h = s->h;
-  const int H = h.hidden, F = h.inter, B = h.batch, V = h.vocab;
+  enqueue_head(s, L);
+  for (uint32_t l = 0; l < h.layers; ++l) enqueue_layer(s, L, s->layers[l]);
+  enqueue_tail(s, L);
+}
+
+void enqueue_layer(State *s, Launcher &L, const Layer &ly) {
+  const QwenHeader &h = s->h;
+  const int H = h.hidden, F = h.inter, B = h.batch;
   const int QD = h.n_q * 64, KVD = h.n_kv * 64, QKV = QD + 2 * KVD;
   const int pdl = (h.flags & 1) ? 1 : 0;
-  EmbedArgs ea{H, B, 1, V};
-  L("embed_gather", {s->embed, s->meta, s->hA}, ea, (H + 255) / 256, B, 1, 256, 0, pdl);
-  for (uint32_t l = 0; l < h.layers; ++l) {
-    const Layer &ly = s->layers[l];
+  {
     GemvArgs gq{QKV, H, B, 0, h.eps, 1, 1, H, QKV, 1};
     launch_gemv(s, L, {ly.wqkv, ly.bqkv, s->hA, ly.ln1, -1, -1, -1, -1, s->qkv}, gq, pdl);
     AttnArgs aa{int(h.n_q), int(h.n_kv), 64, B, int(h.max_seq), 0, int(h.max_seq), QKV, 0, 1, 0.125f, s->max_splits};
@@ -118,6 +140,12 @@ void enqueue_step(State *s, Launcher &L) {
     GemvArgs gd{H, F, B, 0, h.eps, 1, 3, 2 * F, H, 1};
     launch_gemv(s, L, {ly.wdn, -1, s->gu, -1, -1, -1, -1, s->hB, s->hA}, gd, pdl);            // hA = hB + Wd act
   }
+}
+
+void enqueue_tail(State *s, Launcher &L) {
+  const QwenHeader &h = s->h;
+  const int H = h.hidden, B = h.batch, V = h.vocab;
+  const int pdl = (h.flags & 1) ? 1 : 0;
   GemvArgs gl{V, H, B, 0, h.eps, 1, 1, H, V, std::max(1, (V + 8 * 1184 - 1) / (8 * 1184))};
   launch_gemv(s, L, {s->embed, -1, s->hA, s->lnf, -1, -1, -1, -1, s->logits}, gl, pdl);       // tied lm_head
   ArgmaxArgs am{V, B, V, kArgmaxParts};
@@ -162,8 +190,10 @@ void stage_load(uint8_t *mem) {
   if (!ok) return scope.fail(2, std::string("load: allocation failed: ") + cl_b200_last_error());
   synth(L, s->embed, V * H, 1000, kEmbed, h.seed, 2, 0.02);
   synth(L, s->lnf, H, 1000, kLnF, h.seed, 4, 0.02);
-  s->layers.resize(h.layers);
-  for (uint32_t l = 0; l < h.layers && ok && L.ok; ++l) {
+  s->on_disk = (h.flags & 8) ? 1 : 0;
+  const uint32_t resident = s->on_disk ? 1u : h.layers;      // on-disk mode: one working set, filled per layer from the file
+  s->layers.resize(resident);
+  for (uint32_t l = 0; l < resident && ok && L.ok; ++l) {
     Layer &ly = s->layers[l];
     ly.ln1 = alloc(ctx, H * 4, &ok);
     ly.wqkv = alloc(ctx, QKV * H * 4, &ok);
@@ -175,6 +205,7 @@ void stage_load(uint8_t *mem) {
     ly.kcache = alloc(ctx, B * KVD * h.max_seq * 4, &ok);
     ly.vcache = alloc(ctx, B * KVD * h.max_seq * 4, &ok);
     if (!ok) break;
+    if (s->on_disk) continue;
     synth(L, ly.ln1, H, l, kLn1, h.seed, 4, 0.02);
     synth(L, ly.wqkv, QKV * H, l, kWqkv, h.seed, 2, 0.02);
     synth(L, ly.bqkv, QKV, l, kBqkv, h.seed, 2, 0.02);
@@ -241,6 +272,179 @@ bool ensure_graph(State *s, B200CudaContext *ctx, std::string *err) {
   return true;
 }
 
+// ---- on-disk mode (the reference's qwen2_on_disk variant, lean/algorithms/Qwen2OnDiskAlgorithm.lean:18-42: one layer's
+// weight buffers and one K/V pair on the device, reused by all layers; "only the storage strategy differs") ------------
+// Weight file: the reference's flat f32 layout (tools/qwen2_convert.py:12-28).  Cache file: f32
+// [layer][K, V][sequence][kv head][position][64], created by openFiles.
+struct FlatLayout {
+  uint64_t embed, layer0, per_layer, lnf, lm_head, total;            // float offsets
+  uint64_t ln1, wq, bq, wk, bk, wv, bv, wo, ln2, wgate, wup, wdn;    // float offsets inside a layer
+};
+
+FlatLayout flat_layout(const QwenHeader &h) {
+  const uint64_t H = h.hidden, F = h.inter, V = h.vocab, QD = uint64_t(h.n_q) * 64, KVD = uint64_t(h.n_kv) * 64;
+  FlatLayout f{};
+  uint64_t at = 0;
+  f.ln1 = at; at += H;
+  f.wq = at; at += QD * H;
+  f.bq = at; at += QD;
+  f.wk = at; at += KVD * H;
+  f.bk = at; at += KVD;
+  f.wv = at; at += KVD * H;
+  f.bv = at; at += KVD;
+  f.wo = at; at += H * QD;
+  f.ln2 = at; at += H;
+  f.wgate = at; at += F * H;
+  f.wup = at; at += F * H;
+  f.wdn = at; at += H * F;
+  f.per_layer = at;
+  f.embed = 0;
+  f.layer0 = V * H;
+  f.lnf = f.layer0 + uint64_t(h.layers) * f.per_layer;
+  f.lm_head = f.lnf + H;
+  f.total = f.lm_head + V * H;
+  return f;
+}
+
+bool read_all(int fd, void *dst, uint64_t bytes, uint64_t off) {
+  uint8_t *p = static_cast<uint8_t *>(dst);
+  while (bytes) {
+    const ssize_t n = pread(fd, p, size_t(std::min<uint64_t>(bytes, 1u << 30)), off_t(off));
+    if (n <= 0) return false;
+    p += n; off += uint64_t(n); bytes -= uint64_t(n);
+  }
+  return true;
+}
+
+bool write_all(int fd, const void *src, uint64_t bytes, uint64_t off) {
+  const uint8_t *p = static_cast<const uint8_t *>(src);
+  while (bytes) {
+    const ssize_t n = pwrite(fd, p, size_t(bytes), off_t(off));
+    if (n <= 0) return false;
+    p += n; off += uint64_t(n); bytes -= uint64_t(n);
+  }
+  return true;
+}
+
+void close_files(State *s) {
+  if (s->wfd >= 0) close(s->wfd);
+  if (s->kvfd >= 0) close(s->kvfd);
+  s->wfd = s->kvfd = -1;
+}
+
+// openFiles: data = "weights_path\0cache_path\0".  Checks the weight file's size against the header's shapes, loads the
+// embedding (it doubles as lm_head: a file whose lm_head differs is refused) and the final norm, creates the cache file.
+void stage_open_files(uint8_t *mem) {
+  StageIO io(mem);
+  State *s = io.state<State>();
+  if (!s || !s->on_disk) return stage_fail(mem, 1, "openFiles: needs a load with flags bit 3");
+  const char *d = reinterpret_cast<const char *>(io.data);
+  const size_t n = size_t(io.data_len);
+  const size_t l1 = n ? strnlen(d, n) : 0;
+  if (l1 == 0 || l1 + 1 >= n || d[n - 1] != 0) return stage_fail(mem, 1, "openFiles: data must be two NUL-terminated paths");
+  const char *wpath = d, *kvpath = d + l1 + 1;
+  B200CudaContext *ctx = io.ctx();
+  const QwenHeader &h = s->h;
+  const FlatLayout f = flat_layout(h);
+  close_files(s);
+  s->wfd = open(wpath, O_RDONLY);
+  if (s->wfd < 0) return stage_fail(mem, 2, std::string("openFiles: cannot open ") + wpath);
+  struct stat st;
+  if (fstat(s->wfd, &st) != 0 || uint64_t(st.st_size) != f.total * 4) {
+    close_files(s);
+    return stage_fail(mem, 1, "openFiles: the weight file's size does not match the header's shapes");
+  }
+  const uint64_t H = h.hidden, V = h.vocab, emb = V * H * 4;
+  const uint64_t kv_bytes = uint64_t(h.layers) * 2 * h.batch * h.n_kv * h.max_seq * 64 * 4;
+  s->host.resize(size_t(std::max<uint64_t>(f.per_layer * 4, 1u << 20)));
+  // embedding and lm_head, a piece at a time: equal, or the file is not for this (tied) stage program
+  std::vector<uint8_t> other(s->host.size());
+  for (uint64_t off = 0; off < emb; off += s->host.size()) {
+    const uint64_t nb = std::min<uint64_t>(s->host.size(), emb - off);
+    if (!read_all(s->wfd, s->host.data(), nb, f.embed * 4 + off) || !read_all(s->wfd, other.data(), nb, f.lm_head * 4 + off)) {
+      close_files(s);
+      return stage_fail(mem, 2, "openFiles: short read");
+    }
+    if (memcmp(s->host.data(), other.data(), size_t(nb)) != 0) {
+      close_files(s);
+      return stage_fail(mem, 1, "openFiles: lm_head differs from embed_tokens (this stage program ties them)");
+    }
+    if (cl_cuda_upload_ptr_offset(ctx, s->embed, int64_t(off), s->host.data(), int64_t(nb)) != 0) {
+      close_files(s);
+      return stage_fail(mem, 2, std::string("openFiles: ") + cl_b200_last_error());
+    }
+  }
+  if (!read_all(s->wfd, s->host.data(), H * 4, f.lnf * 4) || cl_cuda_upload_ptr(ctx, s->lnf, s->host.data(), int64_t(H * 4)) != 0) {
+    close_files(s);
+    return stage_fail(mem, 2, "openFiles: final norm");
+  }
+  s->kvfd = open(kvpath, O_RDWR | O_CREAT | O_TRUNC, 0600);
+  if (s->kvfd < 0 || ftruncate(s->kvfd, off_t(kv_bytes)) != 0) {
+    close_files(s);
+    return stage_fail(mem, 2, std::string("openFiles: cannot create ") + kvpath);
+  }
+}
+
+// One decode step with the weights and the cache on disk.  Nothing is captured: the host reads a layer's bytes, the
+// synchronous copies (which run on the main stream, after the layer before) fill the working set, the layer's kernels
+// follow, and the stream is drained before the new cache row is read back.
+bool step_on_disk(State *s, B200CudaContext *ctx, std::string *err) {
+  const QwenHeader &h = s->h;
+  if (s->wfd < 0 || s->kvfd < 0) { *err = "openFiles has not run"; return false; }
+  const FlatLayout f = flat_layout(h);
+  const uint64_t H = h.hidden, F = h.inter, QD = uint64_t(h.n_q) * 64, KVD = uint64_t(h.n_kv) * 64;
+  const uint64_t region = uint64_t(h.batch) * h.n_kv * h.max_seq * 64;          // floats of one layer's K (or V)
+  const Layer &ws = s->layers[0];
+  Launcher L{ctx, s->module};
+  enqueue_head(s, L);
+  float *w = reinterpret_cast<float *>(s->host.data());
+  auto up = [&](int buf, uint64_t dst_floats, uint64_t src_floats, uint64_t count) {
+    return cl_cuda_upload_ptr_offset(ctx, buf, int64_t(dst_floats * 4), reinterpret_cast<const uint8_t *>(w + src_floats),
+                                     int64_t(count * 4)) == 0;
+  };
+  std::vector<float> row(64);
+  for (uint32_t l = 0; l < h.layers; ++l) {
+    if (!read_all(s->wfd, w, f.per_layer * 4, (f.layer0 + uint64_t(l) * f.per_layer) * 4)) { *err = "weight file: short read"; return false; }
+    if (cl_cuda_stream_sync(ctx, -1) != 0) { *err = cl_b200_last_error(); return false; }     // the layer before is done with the working set
+    bool ok = up(ws.ln1, 0, f.ln1, H) && up(ws.wqkv, 0, f.wq, QD * H) && up(ws.wqkv, QD * H, f.wk, KVD * H) &&
+              up(ws.wqkv, (QD + KVD) * H, f.wv, KVD * H) && up(ws.bqkv, 0, f.bq, QD) && up(ws.bqkv, QD, f.bk, KVD) &&
+              up(ws.bqkv, QD + KVD, f.bv, KVD) && up(ws.wo, 0, f.wo, H * QD) && up(ws.ln2, 0, f.ln2, H) &&
+              up(ws.wgu, 0, f.wgate, F * H) && up(ws.wgu, F * H, f.wup, F * H) && up(ws.wdn, 0, f.wdn, H * F);
+    // this layer's K/V rows of the positions before the current one
+    const uint64_t kbase = uint64_t(l) * 2 * region, vbase = kbase + region;
+    std::vector<float> past;
+    for (uint32_t b = 0; b < h.batch && ok; ++b) {
+      const uint64_t pos = uint64_t(s->next_pos[b]);
+      if (pos == 0) continue;
+      past.resize(size_t(pos) * 64);
+      for (uint32_t kh = 0; kh < h.n_kv && ok; ++kh) {
+        const uint64_t at = (uint64_t(b) * h.n_kv + kh) * h.max_seq * 64;
+        ok = read_all(s->kvfd, past.data(), pos * 256, (kbase + at) * 4) &&
+             cl_cuda_upload_ptr_offset(ctx, ws.kcache, int64_t(at * 4), reinterpret_cast<const uint8_t *>(past.data()), int64_t(pos * 256)) == 0 &&
+             read_all(s->kvfd, past.data(), pos * 256, (vbase + at) * 4) &&
+             cl_cuda_upload_ptr_offset(ctx, ws.vcache, int64_t(at * 4), reinterpret_cast<const uint8_t *>(past.data()), int64_t(pos * 256)) == 0;
+      }
+    }
+    if (!ok) { *err = std::string("streaming layer ") + std::to_string(l) + ": " + cl_b200_last_error(); return false; }
+    enqueue_layer(s, L, ws);
+    if (!L.ok) { *err = L.err; return false; }
+    if (cl_cuda_stream_sync(ctx, -1) != 0) { *err = cl_b200_last_error(); return false; }
+    // the row this step appended goes back to the file
+    for (uint32_t b = 0; b < h.batch && ok; ++b)
+      for (uint32_t kh = 0; kh < h.n_kv && ok; ++kh) {
+        const uint64_t at = ((uint64_t(b) * h.n_kv + kh) * h.max_seq + uint64_t(s->next_pos[b])) * 64;
+        ok = cl_cuda_download_ptr_offset(ctx, ws.kcache, int64_t(at * 4), reinterpret_cast<uint8_t *>(row.data()), 256) == 0 &&
+             write_all(s->kvfd, row.data(), 256, (kbase + at) * 4) &&
+             cl_cuda_download_ptr_offset(ctx, ws.vcache, int64_t(at * 4), reinterpret_cast<uint8_t *>(row.data()), 256) == 0 &&
+             write_all(s->kvfd, row.data(), 256, (vbase + at) * 4);
+      }
+    if (!ok) { *err = "cache file: write failed"; return false; }
+  }
+  enqueue_tail(s, L);
+  if (!L.ok) { *err = L.err; return false; }
+  return true;
+}
+
 void stage_prep(uint8_t *mem) {
   StageIO io(mem);
   State *s = io.state<State>();
@@ -290,9 +494,13 @@ void stage_infer(uint8_t *mem) {
   if (io.out_len != 0 && io.out_len != ob) return stage_fail(mem, 1, "infer: out must be one u32 per sequence");
   std::string err;
   if (!room_for(s, 1, &err)) return stage_fail(mem, 1, "infer: " + err);
-  if (!ensure_graph(s, ctx, &err)) return stage_fail(mem, 2, "infer: graph capture: " + err);
-  if (cl_cuda_graph_launch(ctx, s->graph, -1) != 0)
-    return stage_fail(mem, 2, std::string("infer: graph launch: ") + cl_b200_last_error());
+  if (s->on_disk) {
+    if (!step_on_disk(s, ctx, &err)) return stage_fail(mem, 2, "infer: " + err);
+  } else {
+    if (!ensure_graph(s, ctx, &err)) return stage_fail(mem, 2, "infer: graph capture: " + err);
+    if (cl_cuda_graph_launch(ctx, s->graph, -1) != 0)
+      return stage_fail(mem, 2, std::string("infer: graph launch: ") + cl_b200_last_error());
+  }
   for (int64_t &p : s->next_pos) p += 1;
   uint8_t *pout = reinterpret_cast<uint8_t *>(cl_cuda_pinned_ptr(ctx, s->pin_out));
   cl_cuda_download_ptr_async(ctx, s->status, pout + 32, 4, -1);
@@ -318,15 +526,22 @@ void stage_decode(uint8_t *mem) {
     return stage_fail(mem, 1, "decode: out must be empty, tokens, or tokens + 4 bytes");
   std::string err;
   if (!room_for(s, n, &err)) return stage_fail(mem, 1, "decode: " + err);
-  if (!ensure_graph(s, ctx, &err)) return stage_fail(mem, 2, "decode: graph capture: " + err);
+  if (!s->on_disk && !ensure_graph(s, ctx, &err)) return stage_fail(mem, 2, "decode: graph capture: " + err);
   const int64_t row = int64_t(s->h.batch) * 4;
   cl_cuda_event_record(ctx, s->ev0, -1);
-  for (uint32_t i = 0; i < n; ++i)
-    if (cl_cuda_graph_launch(ctx, s->graph, -1) != 0 ||
-        cl_b200_copy_async(ctx, s->tokens_out, int64_t(i) * row, s->next_tok, 0, row, -1) != 0)
+  for (uint32_t i = 0; i < n; ++i) {
+    if (s->on_disk) {
+      if (!step_on_disk(s, ctx, &err)) return stage_fail(mem, 2, "decode: " + err);
+      for (int64_t &p : s->next_pos) p += 1;                 // the next step's cache rows depend on it
+    } else if (cl_cuda_graph_launch(ctx, s->graph, -1) != 0) {
       return stage_fail(mem, 2, std::string("decode: launch: ") + cl_b200_last_error());
+    }
+    if (cl_b200_copy_async(ctx, s->tokens_out, int64_t(i) * row, s->next_tok, 0, row, -1) != 0)
+      return stage_fail(mem, 2, std::string("decode: launch: ") + cl_b200_last_error());
+  }
   cl_cuda_event_record(ctx, s->ev1, -1);
-  for (int64_t &p : s->next_pos) p += n;
+  if (!s->on_disk)
+    for (int64_t &p : s->next_pos) p += n;
   if (cl_cuda_stream_sync(ctx, -1) != 0) return stage_fail(mem, 3, std::string("decode: sync: ") + cl_b200_last_error());
   int32_t st = 0;
   if (cl_cuda_download_ptr(ctx, s->status, reinterpret_cast<uint8_t *>(&st), 4) != 0 || st != 0)
@@ -359,7 +574,7 @@ void stage_fetch_tensor(uint8_t *mem) {
   memcpy(q, io.data, 8);
   int buf = -1;
   if (q[0] == 1000) buf = q[1] == kEmbed ? s->embed : q[1] == kLnF ? s->lnf : -1;
-  else if (q[0] < s->h.layers) {
+  else if (q[0] < s->layers.size()) {      // on-disk mode: only the working set (layer 0) is resident
     const Layer &ly = s->layers[q[0]];
     const int t[] = {ly.ln1, ly.wqkv, ly.bqkv, ly.wo, ly.ln2, ly.wgu, ly.wdn};
     if (q[1] < 7) buf = t[q[1]];
@@ -383,7 +598,7 @@ void stage_set_tensor(uint8_t *mem) {
   memcpy(q, io.data, 8);
   int buf = -1;
   if (q[0] == 1000) buf = q[1] == kEmbed ? s->embed : q[1] == kLnF ? s->lnf : -1;
-  else if (q[0] < s->h.layers) {
+  else if (q[0] < s->layers.size()) {      // on-disk mode: only the working set (layer 0) is resident
     const Layer &ly = s->layers[q[0]];
     const int t[] = {ly.ln1, ly.wqkv, ly.bqkv, ly.wo, ly.ln2, ly.wgu, ly.wdn};
     if (q[1] < 7) buf = t[q[1]];
@@ -400,6 +615,7 @@ void destroy(uint8_t *mem) {
   State *s = io.state<State>();
   if (s) {
     if (s->graph >= 0) s->scope.graphs.push_back(s->graph);
+    close_files(s);
     s->scope.release();
     delete s;
     io.set_state(nullptr);
@@ -412,7 +628,8 @@ struct Registrar {
     p.name = "qwen2";
     p.stages = {{"", stage_noop},       {"load", stage_load},     {"prep", stage_prep},
                 {"infer", stage_infer}, {"decode", stage_decode}, {"fetchLogits", stage_fetch_logits},
-                {"fetchTensor", stage_fetch_tensor}, {"setTensor", stage_set_tensor}};
+                {"fetchTensor", stage_fetch_tensor}, {"setTensor", stage_set_tensor},
+                {"openFiles", stage_open_files}};
     p.destroy = destroy;
     register_plugin(p);
   }

@@ -3,6 +3,7 @@ load header and a driver with the reference's decode protocol
 (lean/algorithms/Qwen2Common.lean:30, 830-864).  Host logic only."""
 from __future__ import annotations
 
+import os
 import struct
 from dataclasses import dataclass
 
@@ -44,6 +45,8 @@ class Qwen2Config:
         return self.layers * per_layer + self.vocab * H * 4 + self.layers * self.batch * ctx_len * 2 * kvd * 4
 
 
+ON_DISK = 8      # header flags bit 3: one layer's weights and one K/V pair on the device, the rest on disk (open_files)
+
 QWEN2_0_5B = Qwen2Config()
 
 
@@ -84,6 +87,11 @@ class Qwen2:
         out = bytearray(count * 4)
         self.base.execute_into(self.art.extras["fetchTensor"], struct.pack("<2I", layer, KIND[kind]), out)
         return np.frombuffer(bytes(out), dtype="<f4")
+
+    def open_files(self, weights_path: str, cache_path: str) -> None:
+        """ON_DISK instances: the flat f32 weight file to stream the layers from (base_b200.convert.write_qwen2_flat) and
+        the file to keep the KV cache in (created here); before the first step."""
+        self.base.execute(self.art.extras["openFiles"], os.fsencode(weights_path) + b"\0" + os.fsencode(cache_path) + b"\0")
 
     def set_tensor(self, layer: int, kind: str, values) -> None:
         """Replace a seeded tensor by real f32 weights (stage `setTensor`; layout as `tensor` returns it)."""

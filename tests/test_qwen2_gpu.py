@@ -173,3 +173,52 @@ def test_weights_from_a_flat_file_replace_the_seeded_ones(tmp_path):
         m.base.execute(m.art.extras["setTensor"], b"\x07\x00\x00\x00\x09\x00\x00\x00" + b"\0" * 4)
     m.close()
     del seeded
+
+
+def test_on_disk_mode_decodes_exactly_like_the_resident_model(tmp_path):
+    """The reference's second storage strategy (one layer's weights and one K/V pair on the device, the layers streamed
+    from the weight file and the cache kept in a file, Qwen2OnDiskAlgorithm.lean:18-42) must give byte-identical output
+    (applications/qwen2/tests/golden_cli.rs:1-8): same tokens and bit-equal logits as the resident model, fed step by
+    step and with the argmax fed back on the device."""
+    from base_b200 import convert as cv
+    from base_b200.qwen2 import ON_DISK
+    c = small(layers=3, vocab=320, max_seq=40)
+    m = Qwen2(c)
+    QD, KVD, F = c.n_q * 64, c.n_kv * 64, c.inter
+    flat = {("embed", None): m.tensor(1000, "embed", c.vocab * c.hidden).reshape(c.vocab, c.hidden),
+            ("lnf", None): m.tensor(1000, "lnf", c.hidden)}
+    flat[("lm_head", None)] = flat[("embed", None)]
+    for l in range(c.layers):
+        wqkv = m.tensor(l, "wqkv", (QD + 2 * KVD) * c.hidden).reshape(QD + 2 * KVD, c.hidden)
+        bqkv = m.tensor(l, "bqkv", QD + 2 * KVD)
+        wgu = m.tensor(l, "wgu", 2 * F * c.hidden).reshape(2 * F, c.hidden)
+        flat.update({("ln1", l): m.tensor(l, "ln1", c.hidden), ("wq", l): wqkv[:QD], ("wk", l): wqkv[QD:QD + KVD],
+                     ("wv", l): wqkv[QD + KVD:], ("bq", l): bqkv[:QD], ("bk", l): bqkv[QD:QD + KVD], ("bv", l): bqkv[QD + KVD:],
+                     ("wo", l): m.tensor(l, "wo", c.hidden * QD).reshape(c.hidden, QD), ("ln2", l): m.tensor(l, "ln2", c.hidden),
+                     ("wgate", l): wgu[:F], ("wup", l): wgu[F:],
+                     ("wdn", l): m.tensor(l, "wdn", c.hidden * F).reshape(c.hidden, F)})
+    wpath, kvpath = tmp_path / "w.bin", tmp_path / "kv.bin"
+    cv.write_qwen2_flat(wpath, c, flat)
+    import dataclasses
+    d = Qwen2(dataclasses.replace(c, flags=c.flags | ON_DISK))
+    with pytest.raises(RuntimeError, match="openFiles has not run"):
+        d.infer([5], [0])
+    d.open_files(str(wpath), str(kvpath))
+    assert kvpath.stat().st_size == c.layers * 2 * c.n_kv * c.max_seq * 64 * 4
+    tok = 5
+    for pos in range(5):
+        a, b = int(m.infer([tok], [pos])[0]), int(d.infer([tok], [pos])[0])
+        assert a == b
+        np.testing.assert_array_equal(m.logits(), d.logits())
+        tok = a
+    m.prep([tok], [5])
+    d.prep([tok], [5])
+    np.testing.assert_array_equal(m.decode(6), d.decode(6))                      # device feedback, cache rows through the file
+    kv = np.fromfile(kvpath, dtype="<f4").reshape(c.layers, 2, c.n_kv, c.max_seq, 64)
+    assert np.abs(kv[:, :, :, :11]).max(axis=-1).min() > 0 and not kv[:, :, :, 11:].any()    # 11 positions written, the rest untouched
+    other = Qwen2(dataclasses.replace(c, layers=2, flags=c.flags | ON_DISK))
+    with pytest.raises(RuntimeError, match="size does not match"):
+        other.open_files(str(wpath), str(kvpath))
+    other.close()
+    m.close()
+    d.close()
