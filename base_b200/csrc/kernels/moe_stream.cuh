@@ -50,7 +50,7 @@ B200_DEVICE bool mbar_wait(uint64_t *bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
   return false;
 }
-// Plain (non-multicast) bulk copy global -> this CTA's shared memory.
+// Plain bulk copy global -> this CTA's shared memory (one destination CTA).
 B200_DEVICE void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                    smem_u32(dst)),
